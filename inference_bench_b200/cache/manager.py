@@ -3,7 +3,9 @@ with the same needs, and beside them slots of fixed-size per-request state.
 
 Executions of the schedule whose mixers ask for the same `PagedKV(kv_heads, head_dim, window)` form a
 group. A group has its own page pool, its own device tensor
-[executions, pages, 2 (K, V), kv_heads, page_size, head_dim] and its own block table per request; a
+[executions, pages, 2 (K, V), kv_heads, page_size, head_dim] and its own block table per request
+(`PagedRows(width, window)`, one row per token, is the same with one plane and one head:
+[executions, pages, 1, 1, page_size, width]); a
 page therefore holds `page_size` positions of every execution in the group, and one table serves
 them all (block-major, like the reference: docs/specrt-scheduler.md:11, 20-22). A group with a window
 gives a page back as soon as every position in it has fallen out of the window of the request's
@@ -24,7 +26,7 @@ import ctypes as C
 
 import numpy as np
 
-from ..parts.base import FixedState, PagedKV
+from ..parts.base import FixedState, PagedKV, PagedRows
 from . import native
 from .pages import PagePool
 
@@ -39,7 +41,7 @@ class CacheError(RuntimeError):
 
 @dataclass
 class Group:
-    need: PagedKV
+    need: Any                   # PagedKV or PagedRows
     entries: list[int]          # schedule entries whose keys and values live in this group's pages
     pool: PagePool
     tensor: Any = None          # device tensor, None without a device
@@ -100,9 +102,9 @@ class CacheManager:
         self.groups: list[Group] = []
         self.place: dict[int, tuple[int, int]] = {}    # schedule entry -> (group index, index inside the page)
         self.states: dict[int, StateView] = {}         # schedule entry -> fixed state
-        by_need: dict[PagedKV, int] = {}
+        by_need: dict[Any, int] = {}
         for i, need in enumerate(needs):
-            if isinstance(need, PagedKV):
+            if isinstance(need, (PagedKV, PagedRows)):
                 g = by_need.get(need)
                 if g is None:
                     g = by_need[need] = len(self.groups)
@@ -129,7 +131,8 @@ class CacheManager:
             for g in self.groups:
                 n = g.need
                 # one page more than the pool hands out: the scratch page that padded rows of a fixed-size batch write to
-                g.tensor = torch.zeros((len(g.entries), g.pool.num_pages + 1, 2, n.kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
+                planes, heads, width = (2, n.kv_heads, n.head_dim) if isinstance(n, PagedKV) else (1, 1, n.width)
+                g.tensor = torch.zeros((len(g.entries), g.pool.num_pages + 1, planes, heads, page_size, width), dtype=dtype, device=device)
             for i, n in self._fixed.items():
                 # and one scratch slot more than requests can hold
                 self.states[i].tensor = torch.zeros((max_requests + 1, *n.shape), dtype=n.dtype, device=device)

@@ -258,6 +258,43 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, int P, size_t stri
   }
 }
 
+// ---------------------------------------------------------------- norm of a sublayer's output, added to the residual stream
+// One block per row t:  y = sum_p delta[p][t];  x[t] += mult * w * (y * rsqrt(mean(y^2) + eps));  act[t] = x[t] in the
+// activation dtype (what the next sublayer reads), when act is given. The row of y lives in shared memory between the passes.
+template <typename O>
+__global__ void norm_residual_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride, const float* __restrict__ w,
+                                     float mult, float eps, O* __restrict__ act, int H) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float scratch[32];
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int t = blockIdx.x;
+  const float* dr = delta + (size_t)t * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float d = dr[i];
+    for (int p = 1; p < P; p++) d += dr[p * delta_stride + i];
+    row[i] = d;
+    ss += d * d;
+  }
+  ss = ib::block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)H + eps);
+  float* xr = x + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = xr[i] + mult * (w[i] * (row[i] * inv));
+    xr[i] = v;
+    if (act) act[(size_t)t * H + i] = ib::from_f32<O>(v);
+  }
+}
+
+// act[t] = x[t] in another dtype.
+template <typename O>
+__global__ void cast_rows_kernel(const float* __restrict__ x, O* __restrict__ act, size_t n) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) act[i] = ib::from_f32<O>(x[i]);
+}
+
 }  // namespace
 
 extern "C" int ib_embed(const void* table, int table_dtype, const int* tokens, float* x, int T, int H, int V, unsigned* status,
@@ -344,5 +381,34 @@ extern "C" int ib_silu_mul(const float* gu, int P, long long stride, void* act, 
   else
     return ib_set_error("silu_mul: unknown output dtype %d", act_dtype);
   IB_CHECK_LAUNCH("silu_mul");
+  return 0;
+}
+
+extern "C" int ib_norm_residual(float* x, const float* delta, int P, long long delta_stride, const float* w, float mult, float eps, void* act, int act_dtype,
+                                int T, int H, cudaStream_t stream) {
+  if (T == 0) return 0;
+  IB_CHECK_ARG(T > 0 && H > 0 && P >= 1 && delta, "norm_residual: bad sizes T=%d H=%d P=%d", T, H, P);
+  const size_t smem = (size_t)H * sizeof(float);
+  IB_CHECK_ARG(smem <= 200 * 1024, "norm_residual: hidden size %d needs %zu bytes of shared memory, more than 200 KiB", H, smem);
+  const int threads = H >= 2048 ? 1024 : (H >= 1024 ? 512 : 256);
+  auto go = [&](auto kernel, auto* a) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ib::launch(kernel, T, threads, smem, stream, x, delta, P, (size_t)delta_stride, w, mult, eps, a, H);
+  };
+  if (!act || act_dtype == IB_F32) go(norm_residual_kernel<float>, (float*)act);
+  else if (act_dtype == IB_BF16) go(norm_residual_kernel<__nv_bfloat16>, (__nv_bfloat16*)act);
+  else return ib_set_error("norm_residual: unknown activation dtype %d", act_dtype);
+  IB_CHECK_LAUNCH("norm_residual");
+  return 0;
+}
+
+extern "C" int ib_cast_rows(const float* x, void* act, int act_dtype, long long n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  IB_CHECK_ARG(n > 0, "cast_rows: bad size %lld", n);
+  const unsigned blocks = (unsigned)((n + 255) / 256 > 4096 ? 4096 : (n + 255) / 256);
+  if (act_dtype == IB_BF16) ib::launch(cast_rows_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, (__nv_bfloat16*)act, (size_t)n);
+  else if (act_dtype == IB_F32) ib::launch(cast_rows_kernel<float>, blocks, 256, 0, stream, x, (float*)act, (size_t)n);
+  else return ib_set_error("cast_rows: unknown dtype %d", act_dtype);
+  IB_CHECK_LAUNCH("cast_rows");
   return 0;
 }

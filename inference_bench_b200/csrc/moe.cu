@@ -1,0 +1,328 @@
+// Routed feed-forward (mixture of experts): the router's choice, the regrouping of the step's tokens by expert,
+// the experts' matrix products on the regrouped rows, and the weighted sum back into token order.
+//
+//  * moe_route: per token, s = softmax(router logits) over all experts in float32; experts lie in `n_groups` equal
+//    groups of neighbours, a group's score is its largest s, only the `keep` best groups stay eligible; the `top`
+//    eligible experts with the largest s are chosen (ties: the lower index), each weighted s * route_scale, or
+//    s / (sum of the chosen s) * route_scale with `renorm`.
+//  * moe_sort: counts the (token, choice) pairs of every expert, lays the experts' rows out one after the other
+//    (offsets[e] .. offsets[e + 1]) and gives every pair its row; tile_start[e] is the first 64-row tile of expert e.
+//  * gemm_grouped: out[r] = W[e(r)] x[src(r)] for every regrouped row r: a 64 x 64 tile belongs to one expert; float32
+//    FMA chains per output (a row's result does not depend on its place among the rows). With `gated`, W holds gate
+//    rows then up rows and the output is silu(gate) * up.
+//  * moe_combine: out[t] = sum_p base[p][t] + sum_k weight[t][k] * y[row(t, k)], in the order of the choices.
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kRouteWarps = 4;
+
+// (value, index) argmax over a warp: larger value wins, then the lower index.
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) v = ov, i = oi;
+  }
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int P, size_t stride_p, int T, int E, int n_groups, int keep, int top, float route_scale,
+                                 int renorm, int* __restrict__ idx_out, float* __restrict__ wt_out) {
+  extern __shared__ float sm[];   // per warp: E scores, then n_groups group scores
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  if (t >= T) return;
+  float* s = sm + (size_t)warp * (E + n_groups);
+  float* g = s + E;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) {
+    float z = logits[(size_t)t * E + e];
+    for (int p = 1; p < P; p++) z += logits[p * stride_p + (size_t)t * E + e];
+    s[e] = z;
+    mx = fmaxf(mx, z);
+  }
+  mx = ib::warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = expf(s[e] - mx);
+    s[e] = v;
+    sum += v;
+  }
+  sum = ib::warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int e = lane; e < E; e += 32) s[e] *= inv;
+  __syncwarp();
+  if (n_groups > 1 && keep < n_groups) {
+    const int per = E / n_groups;
+    for (int k = lane; k < n_groups; k += 32) {
+      float b = -1.f;
+      for (int e = k * per; e < (k + 1) * per; e++) b = fmaxf(b, s[e]);
+      g[k] = b;
+    }
+    __syncwarp();
+    for (int r = 0; r < keep; r++) {   // the best groups, one after the other; a kept group's score becomes -2
+      float bv = -1.5f;
+      int bi = 0x7fffffff;
+      for (int k = lane; k < n_groups; k += 32)
+        if (g[k] > bv) bv = g[k], bi = k;
+      warp_argmax(bv, bi);
+      if (lane == 0 && bi < n_groups) g[bi] = -2.f;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (g[e / per] != -2.f) s[e] = -1.f;   // not eligible
+    __syncwarp();
+  }
+  float chosen_sum = 0.f;
+  for (int r = 0; r < top; r++) {
+    float bv = -0.5f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (s[e] > bv) bv = s[e], bi = e;
+    warp_argmax(bv, bi);
+    if (bi >= E) bi = 0, bv = 0.f;   // fewer eligible experts than choices: weight zero
+    if (lane == 0) {
+      idx_out[(size_t)t * top + r] = bi;
+      wt_out[(size_t)t * top + r] = bv;
+      s[bi] = -1.f;
+    }
+    chosen_sum += bv;
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float f = renorm ? route_scale / (chosen_sum > 0.f ? chosen_sum : 1.f) : route_scale;
+    for (int r = 0; r < top; r++) wt_out[(size_t)t * top + r] *= f;
+  }
+}
+
+constexpr int SM_ = 64;   // rows of a tile of the grouped product
+
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, int R, int top, int E, int* __restrict__ offsets, int* __restrict__ tile_start,
+                                                        int* __restrict__ row_of_pair, int* __restrict__ token_of_row) {
+  extern __shared__ int si[];   // counts[E], fill[E], start[E + 1]
+  int* counts = si;
+  int* fill = si + E;
+  int* start = si + 2 * E;
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0, fill[e] = 0;
+  __syncthreads();
+  for (int r = threadIdx.x; r < R; r += blockDim.x) {
+    const int e = idx[r];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int a = 0, tl = 0;
+    for (int e = 0; e < E; e++) {
+      start[e] = a;
+      offsets[e] = a;
+      tile_start[e] = tl;
+      a += counts[e];
+      tl += (counts[e] + SM_ - 1) / SM_;
+    }
+    start[E] = a;
+    offsets[E] = a;
+    tile_start[E] = tl;
+  }
+  __syncthreads();
+  // A pair's row inside its expert's range is its rank among the expert's pairs in pair order, so the layout does not
+  // depend on the order threads run in: thread r counts the earlier pairs of the same expert in its own 1024-block by
+  // a shared scan per round.
+  for (int r0 = 0; r0 < R; r0 += blockDim.x) {
+    const int r = r0 + threadIdx.x;
+    int e = -1, before = 0;
+    if (r < R) {
+      e = idx[r];
+      if (e < 0 || e >= E) e = -1;
+    }
+    // rank inside this round: count lower threads with the same expert (warp ballot, then per-warp prefix through fill)
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int lane = threadIdx.x & 31;
+    before = __popc(peers & ((1u << lane) - 1u));
+    const int in_warp = __popc(peers);
+    const bool leader = before == 0;
+    // warps take their turn in order, so that earlier warps' pairs come first
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) {
+      if ((int)(threadIdx.x >> 5) == w && e >= 0) {
+        int base = 0;
+        if (leader) {
+          base = fill[e];
+          fill[e] = base + in_warp;
+        }
+        base = __shfl_sync(peers, base, __ffs(peers) - 1);
+        const int row = start[e] + base + before;
+        row_of_pair[r] = row;
+        token_of_row[row] = r / top;
+      }
+      __syncthreads();
+    }
+  }
+}
+
+template <typename X, typename W, typename O>
+__global__ void __launch_bounds__(256) gemm_grouped_kernel(const X* __restrict__ x, const int* __restrict__ src_row, const W* __restrict__ w,
+                                                           O* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tile_start, int E,
+                                                           int N, int K, int gated) {
+  constexpr int BK = 16;
+  __shared__ float xs[BK][SM_ + 1];
+  __shared__ float ws[BK][64 + 1];
+  __shared__ float us[BK][64 + 1];
+  __shared__ int s_e, s_r0, s_r1;
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  if (threadIdx.x == 0) {
+    const int b = blockIdx.y;
+    int e = -1;
+    if (b < tile_start[E]) {
+      int lo = 0, hi = E;   // the last e with tile_start[e] <= b
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tile_start[mid] <= b) lo = mid;
+        else hi = mid;
+      }
+      e = lo;
+    }
+    s_e = e;
+    if (e >= 0) {
+      s_r0 = offsets[e] + (b - tile_start[e]) * SM_;
+      s_r1 = offsets[e + 1];
+    }
+  }
+  __syncthreads();
+  const int e = s_e;
+  if (e < 0) return;
+  const int r0 = s_r0, r1 = s_r1, n0 = blockIdx.x * 64;
+  const int rows_w = gated ? 2 * N : N;
+  const W* we = w + (size_t)e * rows_w * K;
+  const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
+  float acc[4][4], acu[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.f, acu[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const int idx = tid + q * 256, r = idx / BK, kk = idx % BK, k = k0 + kk;
+      const int row = r0 + r, n = n0 + r;
+      float xv = 0.f;
+      if (row < r1 && k < K) {
+        const int src = src_row ? src_row[row] : row;
+        xv = ib::to_f32<X>(x[(size_t)src * K + k]);
+      }
+      xs[kk][r] = xv;
+      ws[kk][r] = (n < N && k < K) ? ib::to_f32<W>(we[(size_t)n * K + k]) : 0.f;
+      if (gated) us[kk][r] = (n < N && k < K) ? ib::to_f32<W>(we[(size_t)(N + n) * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      float a[4], c[4], u[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = xs[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) c[j] = ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], c[j], acc[i][j]);
+      if (gated) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) u[j] = us[kk][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acu[i][j] = fmaf(a[i], u[j], acu[i][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int row = r0 + ty * 4 + i;
+    if (row >= r1) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if (gated) {
+        v = (v / (1.f + expf(-v))) * acu[i][j];
+      }
+      out[(size_t)row * N + n] = ib::from_f32<O>(v);
+    }
+  }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair, const float* __restrict__ wt, int top,
+                                   const float* __restrict__ base, int P, size_t stride_p, float* __restrict__ out, int H) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int t = blockIdx.y;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) {
+    float a = 0.f;
+    for (int p = 0; p < P; p++) a += base[p * stride_p + (size_t)t * H + i];
+    for (int k = 0; k < top; k++) a = fmaf(wt[(size_t)t * top + k], y[(size_t)row_of_pair[(size_t)t * top + k] * H + i], a);
+    out[(size_t)t * H + i] = a;
+  }
+}
+
+}  // namespace
+
+extern "C" int ib_moe_route(const float* logits, int P, long long stride_p, int T, int E, int n_groups, int keep, int top, float route_scale, int renorm,
+                            int* idx_out, float* wt_out, cudaStream_t stream) {
+  if (T == 0) return 0;
+  IB_CHECK_ARG(P >= 1 && E > 0 && top > 0 && top <= E, "moe_route: bad sizes P=%d experts=%d top=%d", P, E, top);
+  IB_CHECK_ARG(n_groups >= 1 && E % n_groups == 0 && keep >= 1 && keep <= n_groups, "moe_route: %d experts in %d groups of which %d stay", E, n_groups, keep);
+  const size_t smem = (size_t)kRouteWarps * (E + n_groups) * sizeof(float);
+  IB_CHECK_ARG(smem <= 48 * 1024, "moe_route: %d experts need %zu bytes of shared memory, more than 48 KiB", E, smem);
+  ib::launch(moe_route_kernel, (unsigned)((T + kRouteWarps - 1) / kRouteWarps), kRouteWarps * 32, smem, stream, logits, P, (size_t)stride_p, T, E, n_groups, keep,
+             top, route_scale, renorm, idx_out, wt_out);
+  IB_CHECK_LAUNCH("moe_route");
+  return 0;
+}
+
+extern "C" int ib_moe_tile_rows() { return SM_; }
+
+extern "C" int ib_moe_sort(const int* idx, int R, int top, int E, int* offsets, int* tile_start, int* row_of_pair, int* token_of_row, cudaStream_t stream) {
+  if (R == 0) return 0;
+  IB_CHECK_ARG(R > 0 && top > 0 && E > 0, "moe_sort: bad sizes pairs=%d top=%d experts=%d", R, top, E);
+  const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
+  IB_CHECK_ARG(smem <= 48 * 1024, "moe_sort: %d experts need %zu bytes of shared memory, more than 48 KiB", E, smem);
+  ib::launch(moe_sort_kernel, 1, 1024, smem, stream, idx, R, top, E, offsets, tile_start, row_of_pair, token_of_row);
+  IB_CHECK_LAUNCH("moe_sort");
+  return 0;
+}
+
+extern "C" int ib_gemm_grouped(const void* x, int x_dtype, const int* src_row, const void* w, int w_dtype, void* out, int out_dtype, const int* offsets,
+                               const int* tile_start, int R, int E, int N, int K, int gated, cudaStream_t stream) {
+  if (R == 0 || N == 0) return 0;
+  IB_CHECK_ARG(R > 0 && E > 0 && N > 0 && K > 0, "gemm_grouped: bad sizes rows=%d experts=%d N=%d K=%d", R, E, N, K);
+  dim3 grid((N + 63) / 64, R / SM_ + E);   // no more tiles than this, whatever the counts
+  IB_CHECK_ARG(grid.y <= 65535, "gemm_grouped: %d rows exceed the grid limit", R);
+  auto go = [&](auto kernel, auto* xp, auto* wp, auto* op) { ib::launch(kernel, grid, 256, 0, stream, xp, src_row, wp, op, offsets, tile_start, E, N, K, gated); };
+  using bf = __nv_bfloat16;
+  if (x_dtype == IB_F32 && w_dtype == IB_F32 && out_dtype == IB_F32) go(gemm_grouped_kernel<float, float, float>, (const float*)x, (const float*)w, (float*)out);
+  else if (x_dtype == IB_BF16 && w_dtype == IB_BF16 && out_dtype == IB_F32) go(gemm_grouped_kernel<bf, bf, float>, (const bf*)x, (const bf*)w, (float*)out);
+  else if (x_dtype == IB_BF16 && w_dtype == IB_BF16 && out_dtype == IB_BF16) go(gemm_grouped_kernel<bf, bf, bf>, (const bf*)x, (const bf*)w, (bf*)out);
+  else return ib_set_error("gemm_grouped: unsupported dtypes x=%d w=%d out=%d", x_dtype, w_dtype, out_dtype);
+  IB_CHECK_LAUNCH("gemm_grouped");
+  return 0;
+}
+
+extern "C" int ib_moe_combine(const float* y, const int* row_of_pair, const float* wt, int top, const float* base, int P, long long stride_p, float* out, int T,
+                              int H, cudaStream_t stream) {
+  if (T == 0) return 0;
+  IB_CHECK_ARG(T > 0 && H > 0 && top > 0 && P >= 0, "moe_combine: bad sizes T=%d H=%d top=%d P=%d", T, H, top, P);
+  IB_CHECK_ARG(T <= 65535, "moe_combine: T=%d rows exceed the grid limit 65535", T);
+  dim3 grid(min((H + 255) / 256, 64), T);
+  ib::launch(moe_combine_kernel, grid, 256, 0, stream, y, row_of_pair, wt, top, base, P, (size_t)stride_p, out, H);
+  IB_CHECK_LAUNCH("moe_combine");
+  return 0;
+}

@@ -78,7 +78,8 @@ class Engine:
         self.max_ctx = min(max_ctx or DEFAULT_MAX_CTX, limit)   # crates/specrt/src/engine.rs:53-60
         needs = self.decoder.cache_needs()
         if num_pages is None:
-            per_page = sum(2 * n.kv_heads * n.head_dim * page_size for n in needs if hasattr(n, "kv_heads")) * torch.empty(0, dtype=self.rt.act_dtype).element_size()
+            per_token = sum(2 * n.kv_heads * n.head_dim if hasattr(n, "kv_heads") else getattr(n, "width", 0) for n in needs if n is not None and not hasattr(n, "shape"))
+            per_page = per_token * page_size * torch.empty(0, dtype=self.rt.act_dtype).element_size()
             want = max_num_seqs * -(-self.max_ctx // page_size)
             if opts.kv_gb is not None:
                 want = int(opts.kv_gb * 2**30 // max(per_page, 1))

@@ -61,7 +61,7 @@ def kv_tensor_map(pool: torch.Tensor):
     if key not in _KV_MAPS:
         entries, pages, two, kv_heads, page_size, head_dim = pool.shape
         made = None
-        if pool.dtype == torch.bfloat16 and head_dim % 64 == 0 and page_size % 8 == 0 and (64 % page_size == 0 or page_size % 64 == 0):
+        if two == 2 and pool.dtype == torch.bfloat16 and head_dim % 64 == 0 and page_size % 8 == 0 and (64 % page_size == 0 or page_size % 64 == 0):
             buf = C.create_string_buffer(128 + 64)
             addr = (C.addressof(buf) + 63) & ~63
             lib = L.load()
@@ -93,17 +93,17 @@ class KvLayerView:
         return cv
 
     def _make_c_view(self) -> L.KvView:
-        entries, pages, two, kv_heads, page_size, head_dim = self.pool.shape
-        if two != 2:
-            raise L.KernelError(f"a KV pool must be [entries, pages, 2, kv_heads, page_size, head_dim], got {tuple(self.pool.shape)}")
+        entries, pages, planes, kv_heads, page_size, head_dim = self.pool.shape
+        if planes not in (1, 2):
+            raise L.KernelError(f"a cache pool must be [entries, pages, 2 (keys, values) or 1 (rows), kv_heads, page_size, head_dim], got {tuple(self.pool.shape)}")
         _check("kv pool", self.pool)
         _check("block_table", self.block_table, torch.int32)
         per_kv = kv_heads * page_size * head_dim
         esz = self.pool.element_size()
         return L.KvView(
-            base=self.pool.data_ptr() + self.entry * pages * 2 * per_kv * esz,
-            page_stride=2 * per_kv,
-            v_offset=per_kv,
+            base=self.pool.data_ptr() + self.entry * pages * planes * per_kv * esz,
+            page_stride=planes * per_kv,
+            v_offset=per_kv if planes == 2 else 0,
             block_table=self.block_table.data_ptr(),
             table_stride=self.block_table.shape[1],
             page_size=page_size,
@@ -237,3 +237,157 @@ def advance_rows(sampled: torch.Tensor, token_in: torch.Tensor, positions: torch
     _check("count", count, torch.int32, (1,))
     L.call("ib_advance_rows", sampled.data_ptr(), token_in.data_ptr(), positions.data_ptr(), pos0.data_ptr(), params.data_ptr(), history.data_ptr(),
            count.data_ptr(), rows, history.shape[0], _stream())
+
+
+# ---------------------------------------------------------------- norm on a sublayer's output
+L.register("ib_norm_residual", [L._p, L._p, L._i, L._ll, L._p, L._f, L._f, L._p, L._i, L._i, L._i, L._p])
+L.register("ib_cast_rows", [L._p, L._p, L._i, L._ll, L._p])
+
+
+def norm_residual(x: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, mult: float, eps: float, act: Optional[torch.Tensor]) -> None:
+    """x += mult * w * (y * rsqrt(mean(y^2) + eps)) with y = sum_p delta[p] (float32 [P, T, H]); act (optional, [T, H]) = the new x
+    in act's dtype."""
+    T, H = x.shape
+    _check("x", x, torch.float32)
+    _check("w", w, torch.float32, (H,))
+    _check("delta", delta, torch.float32)
+    if delta.dim() != 3 or tuple(delta.shape[1:]) != (T, H):
+        raise L.KernelError(f"delta must be [P, {T}, {H}], got {tuple(delta.shape)}")
+    if act is not None:
+        _check("act", act, None, (T, H))
+    L.call("ib_norm_residual", x.data_ptr(), delta.data_ptr(), delta.shape[0], T * H, w.data_ptr(), float(mult), float(eps), _ptr(act),
+           dtype_code(act.dtype) if act is not None else L.F32, T, H, _stream())
+
+
+def cast_rows(x: torch.Tensor, act: torch.Tensor) -> None:
+    """act = x (float32) in act's dtype."""
+    _check("x", x, torch.float32)
+    _check("act", act, None, tuple(x.shape))
+    L.call("ib_cast_rows", x.data_ptr(), act.data_ptr(), dtype_code(act.dtype), x.numel(), _stream())
+
+
+# ---------------------------------------------------------------- latent attention (csrc/latent_attention.cu)
+L.register("ib_latent_prepare", [L._p, L._i, L._ll, L._i, L._p, L._f, L._p, L._p, L._i, L._p, L._p, L._p, L._i, L._p, C.POINTER(L.KvView), L._i, L._i, L._i, L._i,
+                                 L._i, L._i, L._p, L._p])
+L.register("ib_gemm_heads", [L._p, L._i, L._ll, L._ll, L._p, L._i, L._p, L._i, L._ll, L._ll, L._i, L._i, L._i, L._i, L._p])
+L.register("ib_latent_attention", [L._p, C.POINTER(L.KvView), L._p, L._p, L._f, L._p, L._i, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+L.KERNELS_PER_CALL["ib_latent_attention"] = 1   # two with slices; counted by the caller
+
+
+def latent_prepare(qd: torch.Tensor, c_norm_w: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                   positions: torch.Tensor, seg_of_token: torch.Tensor, q_nope: torch.Tensor, q_full: torch.Tensor, kv: KvLayerView, heads: int, dim: int,
+                   rot: int, rank: int, write_kv: bool, status: torch.Tensor) -> None:
+    """qd float32 [P, T, heads * (dim + rot) (+ rank + rot)]: partial sums of the fused [q | dkv] projection.
+    -> q_nope [T, heads, dim] (activation dtype), q_full[..., rank:] float32 [T, heads, rank + rot] (rotated part), and with
+    write_kv the token's cache row [normed latent | rotated key part]."""
+    _check("qd", qd, torch.float32)
+    P, T, R = qd.shape
+    _check("q_nope", q_nope, None, (T, heads, dim))
+    _check("q_full", q_full, torch.float32, (T, heads, rank + rot))
+    _check("positions", positions, torch.int32, (T,))
+    _check("seg_of_token", seg_of_token, torch.int32, (T,))
+    rot_half = 0
+    if cos is not None:
+        rot_half = cos.shape[1]
+        _check("cos", cos, torch.float32, (T, rot_half))
+        _check("sin", sin, torch.float32, (T, rot_half))
+    if c_norm_w is not None:
+        _check("c_norm_w", c_norm_w, torch.float32, (rank,))
+    view = kv.c_view()
+    L.call("ib_latent_prepare", qd.data_ptr(), P, T * R, R, _ptr(c_norm_w), float(eps), _ptr(cos), _ptr(sin), rot_half, positions.data_ptr(),
+           seg_of_token.data_ptr(), q_nope.data_ptr(), dtype_code(q_nope.dtype), q_full.data_ptr(), C.byref(view), 1 if write_kv else 0, T, heads, dim,
+           rot, rank, status.data_ptr(), _stream())
+
+
+def gemm_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n: int) -> None:
+    """out[t, b, :n] = w[b] x[t, b] for every head b: x [T, heads, K] (contiguous), w [heads, N, K], out [T, heads, >= n] whose
+    first n columns of every head are written (the rest stay)."""
+    T, heads, K = x.shape
+    _check("x", x)
+    _check("w", w, None, (heads, n, K))
+    _check("out", out)
+    if out.dim() != 3 or out.shape[0] != T or out.shape[1] != heads or out.shape[2] < n:
+        raise L.KernelError(f"gemm_heads: out must be [{T}, {heads}, >= {n}], got {tuple(out.shape)}")
+    L.call("ib_gemm_heads", x.data_ptr(), dtype_code(x.dtype), heads * K, K, w.data_ptr(), dtype_code(w.dtype), out.data_ptr(), dtype_code(out.dtype),
+           heads * out.shape[2], out.shape[2], T, heads, n, K, _stream())
+
+
+def latent_attention(q_full: torch.Tensor, kv: KvLayerView, positions: torch.Tensor, seg_of_token: torch.Tensor, scale: float, out: torch.Tensor, rank: int,
+                     n_slices: int, slice_keys: int, scratch, status: torch.Tensor) -> None:
+    """q_full float32 [T, heads, row] against the cached rows [latent (rank) | key part]: out [T, heads, rank] = softmax-weighted sum of
+    the latents of the keys a token sees (all up to its own position). scratch: (part_o, part_ml) float32 when n_slices > 1."""
+    T, heads, D = q_full.shape
+    _check("q_full", q_full, torch.float32)
+    _check("out", out, None, (T, heads, rank))
+    _check("positions", positions, torch.int32, (T,))
+    _check("seg_of_token", seg_of_token, torch.int32, (T,))
+    view = kv.c_view()
+    if view.head_dim != D:
+        raise L.KernelError(f"latent_attention: queries have {D} values, cache rows {view.head_dim}")
+    part_o, part_ml = scratch if scratch is not None else (None, None)
+    if n_slices > 1:
+        _check("part_o", part_o, torch.float32)
+        _check("part_ml", part_ml, torch.float32)
+        if part_o.numel() < T * heads * n_slices * rank or part_ml.numel() < T * heads * n_slices * 2:
+            raise L.KernelError("latent_attention: the scratch for the slices is too small")
+        L.launches += 1
+    L.call("ib_latent_attention", q_full.data_ptr(), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), float(scale), out.data_ptr(),
+           dtype_code(out.dtype), _ptr(part_o), _ptr(part_ml), T, heads, rank, n_slices, slice_keys, status.data_ptr(), _stream())
+
+
+# ---------------------------------------------------------------- routed experts (csrc/moe.cu)
+L.register("ib_moe_route", [L._p, L._i, L._ll, L._i, L._i, L._i, L._i, L._i, L._f, L._i, L._p, L._p, L._p])
+L.register("ib_moe_sort", [L._p, L._i, L._i, L._i, L._p, L._p, L._p, L._p, L._p])
+L.register("ib_gemm_grouped", [L._p, L._i, L._p, L._p, L._i, L._p, L._i, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p])
+L.register("ib_moe_combine", [L._p, L._p, L._p, L._i, L._p, L._i, L._ll, L._p, L._i, L._i, L._p])
+
+
+def moe_route(logits: torch.Tensor, n_groups: int, keep: int, top: int, route_scale: float, renorm: bool, idx: torch.Tensor, wt: torch.Tensor) -> None:
+    """logits float32 [P, T, E] (partial sums) -> idx int32 [T, top], wt float32 [T, top]."""
+    _check("logits", logits, torch.float32)
+    P, T, E = logits.shape
+    _check("idx", idx, torch.int32, (T, top))
+    _check("wt", wt, torch.float32, (T, top))
+    L.call("ib_moe_route", logits.data_ptr(), P, T * E, T, E, n_groups, keep, top, float(route_scale), 1 if renorm else 0, idx.data_ptr(), wt.data_ptr(), _stream())
+
+
+def moe_sort(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, tile_start: torch.Tensor, row_of_pair: torch.Tensor, token_of_row: torch.Tensor) -> None:
+    T, top = idx.shape
+    _check("idx", idx, torch.int32)
+    _check("offsets", offsets, torch.int32, (n_experts + 1,))
+    _check("tile_start", tile_start, torch.int32, (n_experts + 1,))
+    _check("row_of_pair", row_of_pair, torch.int32, (T * top,))
+    _check("token_of_row", token_of_row, torch.int32, (T * top,))
+    L.call("ib_moe_sort", idx.data_ptr(), T * top, top, n_experts, offsets.data_ptr(), tile_start.data_ptr(), row_of_pair.data_ptr(), token_of_row.data_ptr(), _stream())
+
+
+def gemm_grouped(x: torch.Tensor, src_row: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, tile_start: torch.Tensor,
+                 gated: bool) -> None:
+    """out[r] = w[e(r)] x[src_row[r] or r] for the regrouped rows r (expert e's rows are offsets[e]..offsets[e+1]); w [E, N or 2N, K]; with
+    `gated`, w holds gate rows then up rows and out = silu(gate) * up."""
+    R, N = out.shape
+    E, rows_w, K = w.shape
+    if rows_w != (2 * N if gated else N) or x.shape[1] != K:
+        raise L.KernelError(f"gemm_grouped: w {tuple(w.shape)}, x {tuple(x.shape)}, out {tuple(out.shape)} do not fit (gated={gated})")
+    _check("x", x)
+    _check("w", w)
+    _check("out", out)
+    if src_row is not None:
+        _check("src_row", src_row, torch.int32, (R,))
+    L.call("ib_gemm_grouped", x.data_ptr(), dtype_code(x.dtype), _ptr(src_row), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(), dtype_code(out.dtype),
+           offsets.data_ptr(), tile_start.data_ptr(), R, E, N, K, 1 if gated else 0, _stream())
+
+
+def moe_combine(y: torch.Tensor, row_of_pair: torch.Tensor, wt: torch.Tensor, base: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t] = sum_p base[p][t] + sum_k wt[t, k] * y[row_of_pair[t * top + k]]; y float32 [R, H], base float32 [P, T, H] or None."""
+    T, top = wt.shape
+    H = y.shape[1]
+    _check("y", y, torch.float32, (T * top, H))
+    _check("out", out, torch.float32, (T, H))
+    P = 0
+    if base is not None:
+        _check("base", base, torch.float32)
+        if base.dim() != 3 or tuple(base.shape[1:]) != (T, H):
+            raise L.KernelError(f"moe_combine: base must be [P, {T}, {H}], got {tuple(base.shape)}")
+        P = base.shape[0]
+    L.call("ib_moe_combine", y.data_ptr(), row_of_pair.data_ptr(), wt.data_ptr(), top, _ptr(base), P, T * H, out.data_ptr(), T, H, _stream())

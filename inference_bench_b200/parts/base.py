@@ -26,6 +26,7 @@ class WeightSpec:
     """One tensor a part reads by name. `role` decides precision on the device and random init:
     "matrix": kept in bfloat16 unless stored in 32-bit; random ~ N(0, std)
     "norm":   per-channel scale used in float32; random 1 + U(-0.1, 0.1)
+    "norm_offset": the same stored around zero (the scale is 1 + w); random U(-0.2, 0.2)
     "table":  integer table, int32."""
     name: str
     shape: tuple[int, ...]
@@ -43,13 +44,21 @@ class PagedKV:
 
 
 @dataclass(frozen=True)
+class PagedRows:
+    """One row of `width` values for every token of a request, in pages (what latent attention keeps: a
+    compressed latent and a rotated key part that all heads share)."""
+    width: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
 class FixedState:
     """Per-request state of fixed size, zeroed when a request is admitted."""
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
 
 
-CacheNeed = Optional[object]  # PagedKV | FixedState | None
+CacheNeed = Optional[object]  # PagedKV | PagedRows | FixedState | None
 
 
 class Part:
@@ -72,6 +81,11 @@ class Norm(Part):
         source rows are produced and x is left as it is."""
         raise NotImplementedError
 
+    def add_normed(self, ctx: "StepContext", x: torch.Tensor, delta: torch.Tensor, mult: float) -> torch.Tensor:
+        """The norm applied to a sublayer's output instead of its input: x += mult * norm(sum of `delta`), in place
+        (delta: float32 [P, T, H]); returns x in the runtime's activation dtype, for the next sublayer to read."""
+        raise NotImplementedError
+
 
 class PositionEncoding(Part):
     def tables(self, ctx: "StepContext") -> tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
@@ -87,7 +101,7 @@ class Mixer(Part):
 
     def forward(self, ctx: "StepContext", h: torch.Tensor, cache) -> torch.Tensor:
         """h: normalised activations [T, H]; cache: what the cache manager gave this execution
-        (a KvLayerView for PagedKV, a StateView for FixedState, None otherwise).
+        (a KvLayerView for PagedKV and PagedRows, a StateView for FixedState, None otherwise).
         Returns the residual contribution, float32 [P, T, H] (P partial sums, added in order).
         A part with `adds_to_residual` is called with `residual=x` (float32 [T, H]) as well: it may
         add its contribution to x in place and return None, or leave x alone and return the partial sums."""

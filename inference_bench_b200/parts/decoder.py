@@ -31,7 +31,7 @@ class Decoder:
                 raise KeyError(f"no block arrangement {lp.block!r} is registered")
             self.blocks.append(base.BLOCKS[lp.block](
                 _build(base.NORMS, "norm", lp.mixer_norm), _build(base.MIXERS, "mixer", lp.mixer),
-                _build(base.NORMS, "norm", lp.feed_forward_norm), _build(base.FEED_FORWARDS, "feed-forward", lp.feed_forward)))
+                _build(base.NORMS, "norm", lp.feed_forward_norm), _build(base.FEED_FORWARDS, "feed-forward", lp.feed_forward), **dict(lp.block_params)))
         self.final_norm: base.Norm = _build(base.NORMS, "norm", plan.final_norm)
         self.head: base.Head = _build(base.HEADS, "head", plan.head)
         self.rt = None

@@ -1,0 +1,104 @@
+"""Latent attention: keys and values of all heads are linear maps of one small latent per token, and only that latent
+and one rotated key part shared by the heads are cached.
+
+With h the layer's input, per token:
+    q = Wq h, per head [q_n (dim) | q_r (rot_dim)];   [c_raw (kv_rank) | r_raw (rot_dim)] = Wdkv h;
+    c = w_c * c_raw / rms(c_raw),  r = turn(r_raw),  q_r <- turn(q_r)      (pairs 2i, 2i+1; angle pos * base^(-2i/dims))
+    head a:  k = Wuk_a c,  v = Wuv_a c,  s_j = (q_n . k_j + q_r . r_j) * scale  over j <= own position,  o_a = sum_j softmax(s)_j v_j
+    out = Wo [o_1 | o_2 | ...]
+The cache row of a token is [c | r]. The kernels never build k and v: q_n . (Wuk_a c) = (Wuk_a^T q_n) . c and
+sum_j p_j Wuv_a c_j = Wuv_a (sum_j p_j c_j), so a head's query becomes [Wuk_a^T q_n | q_r] against the cached rows, and the
+weighted sum of latents goes through Wuv_a afterwards (two small per-head products around one attention kernel that reads
+kv_rank + rot_dim values a key for all heads together). A layer with own_kv=False has no Wdkv and reads the rows another
+layer cached.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from . import base
+from .base import PagedRows, WeightSpec
+
+
+@base.register_mixer("latent_attention")
+class LatentAttention(base.Mixer):
+    def __init__(self, prefix: str, hidden: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float, norm_eps: float,
+                 position: base.PositionEncoding, own_kv: bool = True, window: Optional[int] = None,
+                 names: tuple = ("q", "dkv", "dkv.norm", "uk", "uv", "o")):
+        if getattr(position, "pairing", "interleaved") != "interleaved":
+            raise ValueError("latent attention turns entry 2i with 2i + 1: it needs a position encoding with pairing=\"interleaved\" (or none)")
+        if window is not None:
+            raise ValueError("latent attention with a window is not built")
+        self.prefix, self.hidden, self.heads, self.dim, self.rot_dim, self.vdim, self.kv_rank = prefix, hidden, heads, dim, rot_dim, vdim, kv_rank
+        self.scale, self.norm_eps, self.position, self.own_kv, self.names = scale, norm_eps, position, own_kv, tuple(names)
+        self.w_in = self.wuk_t = self.wuv = self.wo = self.c_norm = None
+
+    def cache_need(self):
+        return PagedRows(self.kv_rank + self.rot_dim) if self.own_kv else None
+
+    def _name(self, i: int) -> str:
+        return f"{self.prefix}.{self.names[i]}"
+
+    def weight_specs(self):
+        H, r = self.heads, self.kv_rank
+        specs = [WeightSpec(self._name(0), (H * (self.dim + self.rot_dim), self.hidden)), WeightSpec(self._name(3), (H * self.dim, r)),
+                 WeightSpec(self._name(4), (H * self.vdim, r)), WeightSpec(self._name(5), (self.hidden, H * self.vdim))]
+        if self.own_kv:
+            specs += [WeightSpec(self._name(1), (r + self.rot_dim, self.hidden)), WeightSpec(self._name(2), (r,), role="norm")]
+        return specs
+
+    def bind(self, weights, rt):
+        H, r = self.heads, self.kv_rank
+        rows = [weights[self._name(0)]]
+        if self.own_kv:
+            rows.append(weights[self._name(1)])
+            self.c_norm = rt.vector(weights[self._name(2)])
+        self.w_in = rt.matrix(torch.cat(rows, dim=0))   # [q of all heads | latent | key part] rows: one product for the layer's input
+        self.wuk_t = rt.upload(weights[self._name(3)].view(H, self.dim, r).transpose(1, 2), rt.act_dtype)   # [H, rank, dim]: q_n -> rank values
+        self.wuv = rt.upload(weights[self._name(4)].view(H, self.vdim, r), rt.act_dtype)                    # [H, vdim, rank]
+        self.wo = rt.matrix(weights[self._name(5)])
+        self.position.bind(weights, rt)
+
+    def _slices(self, ctx, view) -> tuple[int, int]:
+        """(slices, keys per slice) of the attention kernel: a step of single decoded tokens has few (token, head block)
+        pairs, so each one's keys are cut until every SM has two CTAs; a step with prompt portions has enough rows.
+        The cut depends on the step's sizes (and, outside a captured step, its longest context) only."""
+        key = ("latent slices", self.heads)
+        if key not in ctx.memo:
+            single = ctx.fixed_shape or ctx.max_segment_len == 1
+            out = (1, 1 << 30)
+            if single:
+                max_keys = view.table_stride * view.page_size if ctx.fixed_shape else int(np.max(ctx.h_positions)) + 1
+                ctas = ctx.n_tokens * -(-self.heads // 8)
+                n = max(1, min(2 * ctx.rt.sm_count // ctas, -(-max_keys // 64)))
+                if n > 1:
+                    per = -(-(-(-max_keys // n)) // 32) * 32
+                    out = (-(-max_keys // per), per)
+            ctx.memo[key] = out
+        return ctx.memo[key]
+
+    def forward(self, ctx, h, cache):
+        rt, T, H, r, rot = ctx.rt, ctx.n_tokens, self.heads, self.kv_rank, self.rot_dim
+        cos, sin = self.position.tables(ctx)
+        qd = rt.linear(h, self.w_in)
+        q_nope = rt.empty((T, H, self.dim))
+        q_full = rt.empty((T, H, r + rot), torch.float32)
+        ops.latent_prepare(qd, self.c_norm, self.norm_eps, cos, sin, ctx.positions, ctx.seg_of_token, q_nope, q_full, cache, H, self.dim, rot, r,
+                           self.own_kv, rt.status)
+        ops.gemm_heads(q_nope, self.wuk_t, q_full, r)
+        n_slices, slice_keys = self._slices(ctx, cache.c_view())
+        scratch = None
+        if n_slices > 1:
+            skey = ("latent scratch", H, r, n_slices)
+            if skey not in ctx.memo:
+                ctx.memo[skey] = (rt.empty((T * H * n_slices * r,), torch.float32), rt.empty((T * H * n_slices * 2,), torch.float32))
+            scratch = ctx.memo[skey]
+        u = rt.empty((T, H, r))
+        ops.latent_attention(q_full, cache, ctx.positions, ctx.seg_of_token, self.scale, u, r, n_slices, slice_keys, scratch, rt.status)
+        v = rt.empty((T, H, self.vdim))
+        ops.gemm_heads(u, self.wuv, v, self.vdim)
+        return rt.linear(v.view(T, H * self.vdim), self.wo)

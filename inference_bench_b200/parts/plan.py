@@ -27,6 +27,7 @@ class LayerPlan:
     feed_forward: PartSpec
     mixer_norm: PartSpec
     feed_forward_norm: PartSpec
+    block_params: tuple = ()        # ((name, value), ...): constants of the arrangement itself, e.g. a residual multiplier
 
 
 @dataclass(frozen=True)

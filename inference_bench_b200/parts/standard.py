@@ -22,15 +22,24 @@ class RMSNorm(base.Norm):
     precedes it (crates/kir/tests/golden/rmsnorm_sm120.cu:19-29; no unit offset for this family,
     crates/specrt/src/weights.rs:877-880)."""
 
-    def __init__(self, name: str, size: int, eps: float):
-        self.name, self.size, self.eps = name, size, eps
+    def __init__(self, name: str, size: int, eps: float, unit_offset: bool = False):
+        """unit_offset: the stored weight lies around zero and the scale is 1 + w."""
+        self.name, self.size, self.eps, self.unit_offset = name, size, eps, unit_offset
         self.w: Optional[torch.Tensor] = None
 
     def weight_specs(self):
-        return [WeightSpec(self.name, (self.size,), role="norm")]
+        return [WeightSpec(self.name, (self.size,), role="norm_offset" if self.unit_offset else "norm")]
 
     def bind(self, weights, rt):
         self.w = rt.vector(weights[self.name])
+        if self.unit_offset:
+            self.w = self.w + 1.0   # float32, once: the kernels multiply by the scale whatever it was stored as
+
+    def add_normed(self, ctx, x, delta, mult):
+        rt = ctx.rt
+        act = None if rt.act_dtype == torch.float32 else rt.empty(tuple(x.shape))
+        ops.norm_residual(x, delta, self.w, float(mult), self.eps, act)
+        return x if act is None else act
 
     def forward(self, ctx, x, delta, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
@@ -46,10 +55,14 @@ class RotaryEmbedding(base.PositionEncoding):
     inv_freq_i = theta^(-2i/rotary_dim), angle = float(pos) * inv_freq_i in float32
     (crates/kir/tests/golden/attention/RopeKvWrite_bf16x2_sm120.cu:32-35, 200-206)."""
 
-    def __init__(self, rotary_dim: int, theta: float):
+    def __init__(self, rotary_dim: int, theta: float, pairing: str = "half"):
+        """pairing: which entries a mixer turns together with these angles: "half" pairs entry i with i + rotary_dim/2,
+        "interleaved" pairs entry 2i with 2i + 1. The tables are the same; the mixer's kernel does the pairing."""
         if rotary_dim % 2:
             raise ValueError(f"rotary_dim {rotary_dim} must be even")
-        self.rotary_dim, self.theta = rotary_dim, theta
+        if pairing not in ("half", "interleaved"):
+            raise ValueError(f"pairing {pairing!r} is not known (half, interleaved)")
+        self.rotary_dim, self.theta, self.pairing = rotary_dim, theta, pairing
         self.inv_freq: Optional[torch.Tensor] = None
 
     def bind(self, weights, rt):
@@ -92,6 +105,8 @@ class Attention(base.Mixer):
                  position: base.PositionEncoding, window: Optional[int] = None, own_kv: bool = True, scale: Optional[float] = None):
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
+        if getattr(position, "pairing", "half") != "half":
+            raise ValueError("this attention turns entry i with i + rotary_dim/2: it needs a position encoding with pairing=\"half\"")
         self.prefix, self.hidden, self.heads, self.kv_heads, self.head_dim = prefix, hidden, heads, kv_heads, head_dim
         self.qk_norm, self.norm_eps, self.position, self.window, self.own_kv = qk_norm, norm_eps, position, window, own_kv
         self.scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)  # crates/specrt/src/codegen.rs:147
@@ -154,19 +169,20 @@ class SwiGLU(base.FeedForward):
     (crates/kir/src/cuda/prelude.cu:125-133; gate and up fused into one product at load,
     crates/specrt/src/weights.rs:1049-1062)."""
 
-    def __init__(self, prefix: str, hidden: int, intermediate: int):
-        self.prefix, self.hidden, self.intermediate = prefix, hidden, intermediate
+    def __init__(self, prefix: str, hidden: int, intermediate: int, names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+        """names: what the gate, up and down matrices are called under `prefix`."""
+        self.prefix, self.hidden, self.intermediate, self.names = prefix, hidden, intermediate, tuple(names)
         self.wgu = self.wd = None
 
     def weight_specs(self):
-        p = self.prefix
-        return [WeightSpec(f"{p}.gate_proj.weight", (self.intermediate, self.hidden)), WeightSpec(f"{p}.up_proj.weight", (self.intermediate, self.hidden)),
-                WeightSpec(f"{p}.down_proj.weight", (self.hidden, self.intermediate))]
+        p, (g, u, d) = self.prefix, self.names
+        return [WeightSpec(f"{p}.{g}", (self.intermediate, self.hidden)), WeightSpec(f"{p}.{u}", (self.intermediate, self.hidden)),
+                WeightSpec(f"{p}.{d}", (self.hidden, self.intermediate))]
 
     def bind(self, weights, rt):
-        p = self.prefix
-        self.wgu = rt.matrix(torch.cat([weights[f"{p}.gate_proj.weight"], weights[f"{p}.up_proj.weight"]], dim=0))
-        self.wd = rt.matrix(weights[f"{p}.down_proj.weight"])
+        p, (g, u, d) = self.prefix, self.names
+        self.wgu = rt.matrix(torch.cat([weights[f"{p}.{g}"], weights[f"{p}.{u}"]], dim=0))
+        self.wd = rt.matrix(weights[f"{p}.{d}"])
 
     adds_to_residual = True   # the down projection may add to the residual stream in its epilogue
 
@@ -231,3 +247,51 @@ class PreNormBlock(base.Block):
         a = self.mixer.forward(ctx, h, cache, residual=x) if self.mixer.adds_to_residual else self.mixer.forward(ctx, h, cache)
         h = self.feed_forward_norm.forward(ctx, x, a)
         return self.feed_forward.forward(ctx, h, residual=x) if self.feed_forward.adds_to_residual else self.feed_forward.forward(ctx, h)
+
+
+@base.register_block("outnorm")
+class OutNormBlock(base.Block):
+    """x += m * norm(mixer(x)); x += m * norm(feed_forward(x)): the sublayers read the residual stream itself and the norm
+    sits on what they give back, scaled by a residual multiplier m. The stream stays float32; its rounding to the
+    activation dtype, which the next sublayer reads, is written by the kernel that adds to it. A layer without a
+    feed-forward (`feed_forward` of kind "none") has the first half only."""
+
+    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward, residual_mult: float = 1.0):
+        super().__init__(mixer_norm, mixer, feed_forward_norm, feed_forward)
+        self.residual_mult = residual_mult
+
+    def forward(self, ctx, x, pending, cache):
+        if pending is not None:
+            raise RuntimeError("an outnorm block follows a block that left a contribution to add: mixing arrangements is not supported")
+        key = ("outnorm act", x.data_ptr())
+        h = ctx.memo.get(key)
+        if h is None:   # the first block of a step: the embedding's rows
+            h = x if ctx.rt.act_dtype == torch.float32 else ctx.rt.empty(tuple(x.shape))
+            if h is not x:
+                ops.cast_rows(x, h)
+        a = self.mixer.forward(ctx, h, cache)
+        h = self.mixer_norm.add_normed(ctx, x, a, self.residual_mult)
+        if not isinstance(self.feed_forward, NoFeedForward):
+            f = self.feed_forward.forward(ctx, h)
+            h = self.feed_forward_norm.add_normed(ctx, x, f, self.residual_mult)
+        ctx.memo[key] = h
+        return None
+
+
+@base.register_feed_forward("none")
+class NoFeedForward(base.FeedForward):
+    """A layer that has a mixer only."""
+
+    def __init__(self):
+        pass
+
+    def forward(self, ctx, h):
+        raise RuntimeError("a layer without a feed-forward has nothing to run")
+
+
+@base.register_norm("none")
+class NoNorm(base.Norm):
+    """The place of a norm in a layer that has nothing to norm there."""
+
+    def __init__(self):
+        pass

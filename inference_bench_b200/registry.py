@@ -43,6 +43,8 @@ def known_architectures() -> list[str]:
 
 def resolve(raw_config: Mapping[str, Any]) -> Architecture:
     names = list(raw_config.get("architectures") or [])
+    if not names and isinstance(raw_config.get("architecture"), str):   # a config.json that names its one architecture in the singular
+        names = [raw_config["architecture"]]
     for n in names[:1] + ([raw_config["model_type"]] if raw_config.get("model_type") else []):
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]

@@ -29,6 +29,8 @@ def random_tensor(spec: WeightSpec, seed: int, device="cpu", dtype=torch.bfloat1
     g.manual_seed(_tensor_seed(seed, spec.name))
     if spec.role == "norm":
         t = 1.0 + (torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32) * 0.2 - 0.1)
+    elif spec.role == "norm_offset":
+        t = torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32) * 0.4 - 0.2
     elif spec.role == "matrix":
         t = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32) * (spec.std if std is None else std)
     else:
