@@ -29,6 +29,17 @@ import torch
 DT = torch.float64
 
 
+def exact(t):
+    return t
+
+
+def bf16(t):
+    """Rounding to bfloat16 and back: passed as `rd` it makes the plain model round where a 16-bit implementation may (the input
+    of every product, queries, cached rows, keys and values, attention outputs, the inner activations of a feed-forward), so
+    that a test can tell rounding from a fault."""
+    return t.to(torch.bfloat16).to(t.dtype)
+
+
 def unit_norm(x: torch.Tensor, eps: float) -> torch.Tensor:
     return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
 
@@ -58,31 +69,31 @@ def silu(z):
     return z * torch.sigmoid(z)
 
 
-def gated_ff(h, gate, up, down):
-    return (silu(h @ gate.T) * (h @ up.T)) @ down.T
+def gated_ff(h, gate, up, down, rd=exact):
+    return rd(silu(h @ gate.T) * (h @ up.T)) @ down.T
 
 
-def latent_kv(h, w: Mapping[str, torch.Tensor], p: str, m: Mapping[str, Any], eps: float, positions):
+def latent_kv(h, w: Mapping[str, torch.Tensor], p: str, m: Mapping[str, Any], eps: float, positions, rd=exact):
     """The two things a layer with its own down-projection leaves for attention: c [n, rank], kr [n, rot]."""
     rank, rot = m["kv_rank"], m["rot_dim"]
     d = h @ w[f"{p}.dkv"].T
     c = norm_plain(d[:, :rank], w[f"{p}.dkv.norm"], eps)
     kr = rotate_pairs(d[:, rank:rank + rot], positions, m["rot"]["base"], m["rot"]["dims"])
-    return c, kr
+    return rd(c), rd(kr)
 
 
-def latent_attention(h, w, p: str, m, c, kr, positions):
+def latent_attention(h, w, p: str, m, c, kr, positions, rd=exact):
     """h [n, width] with the latents c, kr of the same n positions (its own or another layer's)."""
     H, dn, dr, dv = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
     n = h.shape[0]
     q = (h @ w[f"{p}.q"].T).view(n, H, dn + dr).transpose(0, 1)           # [H, n, dn+dr]
-    qn, qr = q[..., :dn], rotate_pairs(q[..., dn:], positions, m["rot"]["base"], m["rot"]["dims"])
-    k = (c @ w[f"{p}.uk"].T).view(n, H, dn).transpose(0, 1)               # [H, n, dn]
-    v = (c @ w[f"{p}.uv"].T).view(n, H, dv).transpose(0, 1)               # [H, n, dv]
+    qn, qr = rd(q[..., :dn]), rd(rotate_pairs(q[..., dn:], positions, m["rot"]["base"], m["rot"]["dims"]))
+    k = rd(c @ w[f"{p}.uk"].T).view(n, H, dn).transpose(0, 1)             # [H, n, dn]
+    v = rd(c @ w[f"{p}.uv"].T).view(n, H, dv).transpose(0, 1)             # [H, n, dv]
     s = (qn @ k.transpose(1, 2) + qr @ kr.T[None]) * m["scale"]           # [H, n, n]
     mask = torch.ones(n, n, dtype=torch.bool).tril()
     s = s.masked_fill(~mask, -math.inf)
-    o = torch.softmax(s, dim=-1) @ v                                      # [H, n, dv]
+    o = rd(torch.softmax(s, dim=-1) @ v)                                  # [H, n, dv]
     return o.transpose(0, 1).reshape(n, H * dv) @ w[f"{p}.o"].T
 
 
@@ -99,27 +110,27 @@ def route(h, router_w, r: Mapping[str, Any]):
     return idx, s.gather(1, idx) * r["scale"]
 
 
-def routed_ff(h, w, p: str, f: Mapping[str, Any]):
+def routed_ff(h, w, p: str, f: Mapping[str, Any], rd=exact):
     idx, wt = route(h, w[f"{p}.router"], f["router"])
     out = torch.zeros(h.shape[0], w[f"{p}.e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for e, a in zip(idx[t].tolist(), wt[t]):
-            out[t] += a * gated_ff(h[t:t + 1], w[f"{p}.e{e}.gate"], w[f"{p}.e{e}.up"], w[f"{p}.e{e}.down"])[0]
+            out[t] += a * gated_ff(h[t:t + 1], w[f"{p}.e{e}.gate"], w[f"{p}.e{e}.up"], w[f"{p}.e{e}.down"], rd)[0]
     if f.get("shared"):
-        out = out + gated_ff(h, w[f"{p}.shared.gate"], w[f"{p}.shared.up"], w[f"{p}.shared.down"])
+        out = out + gated_ff(h, w[f"{p}.shared.gate"], w[f"{p}.shared.up"], w[f"{p}.shared.down"], rd)
     return out
 
 
-def feed_forward(h, w, p: str, f):
+def feed_forward(h, w, p: str, f, rd=exact):
     if f["kind"] == "dense":
-        return gated_ff(h, w[f"{p}.gate"], w[f"{p}.up"], w[f"{p}.down"])
+        return gated_ff(h, w[f"{p}.gate"], w[f"{p}.up"], w[f"{p}.down"], rd)
     if f["kind"] == "moe":
-        return routed_ff(h, w, p, f)
+        return routed_ff(h, w, p, f, rd)
     raise ValueError(f["kind"])
 
 
-def hidden_states(config: Mapping[str, Any], weights: Mapping[str, torch.Tensor], tokens) -> list[torch.Tensor]:
-    """The residual stream [n, width] after the embedding and after every layer."""
+def hidden_states(config: Mapping[str, Any], weights: Mapping[str, torch.Tensor], tokens, rd=exact) -> list[torch.Tensor]:
+    """The residual stream [n, width] after the embedding and after every layer (the stream itself is never rounded)."""
     w = {k: v.to(DT) for k, v in weights.items() if v.is_floating_point()}
     eps, m_res = config["norm"]["eps"], config["residual_mult"]
     tokens = torch.as_tensor(tokens, dtype=torch.long)
@@ -132,17 +143,44 @@ def hidden_states(config: Mapping[str, Any], weights: Mapping[str, torch.Tensor]
             raise ValueError(layer["type"])
         m, p = layer["mixer"], f"l{i}.mix"
         if m.get("kv_from") is None:
-            latents[i] = latent_kv(x, w, p, m, eps, positions)
+            latents[i] = latent_kv(rd(x), w, p, m, eps, positions, rd)
         c, kr = latents[m["kv_from"] if m.get("kv_from") is not None else i]
-        x = x + m_res * norm_offset(latent_attention(x, w, p, m, c, kr, positions), w[f"l{i}.norm1"], eps)
+        x = x + m_res * norm_offset(latent_attention(rd(x), w, p, m, c, kr, positions, rd), w[f"l{i}.norm1"], eps)
         if layer.get("mlp"):
-            x = x + m_res * norm_offset(feed_forward(x, w, f"l{i}.mlp", layer["mlp"]), w[f"l{i}.norm2"], eps)
+            x = x + m_res * norm_offset(feed_forward(rd(x), w, f"l{i}.mlp", layer["mlp"], rd), w[f"l{i}.norm2"], eps)
         states.append(x.clone())
     return states
 
 
-def logits(config, weights, tokens) -> torch.Tensor:
+def logits(config, weights, tokens, rd=exact) -> torch.Tensor:
     """[n, vocab] for every position of one sequence."""
-    x = hidden_states(config, weights, tokens)[-1]
+    x = hidden_states(config, weights, tokens, rd)[-1]
     w = weights
-    return norm_offset(x, w["final.norm"].to(DT), config["norm"]["eps"]) @ w["head"].to(DT).T
+    return rd(norm_offset(x, w["final.norm"].to(DT), config["norm"]["eps"])) @ w["head"].to(DT).T
+
+
+class PlainZabonex:
+    """A model folder read with the tests' own safetensors reader."""
+
+    def __init__(self, model_dir):
+        import json
+        from pathlib import Path
+
+        from plain_qwen3 import argmax_lowest, read_safetensors
+        self._argmax = argmax_lowest
+        self.config = json.loads((Path(model_dir) / "config.json").read_text())
+        self.weights = read_safetensors(Path(model_dir) / "model.safetensors")
+
+    def logits(self, tokens, rd=exact) -> torch.Tensor:
+        return logits(self.config, self.weights, tokens, rd).to(torch.float32)
+
+    def hidden_states(self, tokens, rd=exact):
+        return hidden_states(self.config, self.weights, tokens, rd)
+
+    def greedy(self, tokens, new_tokens: int) -> list[int]:
+        toks, out = list(tokens), []
+        for _ in range(new_tokens):
+            nxt = self._argmax(self.logits(toks)[-1])
+            out.append(nxt)
+            toks.append(nxt)
+        return out
