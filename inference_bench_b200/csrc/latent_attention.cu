@@ -325,6 +325,16 @@ extern "C" int ib_gemm_heads(const void* x, int x_dtype, long long x_row, long l
 
 extern "C" int ib_latent_attention_max_rank() { return 1024; }
 
+// out[row] = the slices' unnormalised partial results of (token, head) `row`, merged and normalised.
+extern "C" int ib_latent_combine(const float* part_o, const float* part_ml, void* out, int out_dtype, int rows, int rank, int n_slices, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (out_dtype == IB_F32) ib::launch(latent_combine_kernel<float>, (unsigned)rows, 128, 0, stream, part_o, part_ml, (float*)out, rank, n_slices);
+  else if (out_dtype == IB_BF16) ib::launch(latent_combine_kernel<__nv_bfloat16>, (unsigned)rows, 128, 0, stream, part_o, part_ml, (__nv_bfloat16*)out, rank, n_slices);
+  else return ib_set_error("latent_combine: unknown output dtype %d", out_dtype);
+  IB_CHECK_LAUNCH("latent_combine");
+  return 0;
+}
+
 extern "C" int ib_latent_attention(const float* q, const IbKvView* kv, const int* positions, const int* seg_of_token, float scale, void* out,
                                    int out_dtype, float* part_o, float* part_ml, int T, int heads, int rank, int n_slices, int slice_keys,
                                    unsigned* status, cudaStream_t stream) {
@@ -356,10 +366,6 @@ extern "C" int ib_latent_attention(const float* q, const IbKvView* kv, const int
   else if (out_dtype == IB_BF16 && kv->dtype == IB_BF16) pick(__nv_bfloat16(), (__nv_bfloat16*)out);
   else return ib_set_error("latent_attention: output dtype %d and cache dtype %d must match", out_dtype, kv->dtype);
   IB_CHECK_LAUNCH("latent_attention");
-  if (n_slices > 1) {
-    if (out_dtype == IB_F32) ib::launch(latent_combine_kernel<float>, (unsigned)(T * heads), 128, 0, stream, (const float*)part_o, (const float*)part_ml, (float*)out, rank, n_slices);
-    else ib::launch(latent_combine_kernel<__nv_bfloat16>, (unsigned)(T * heads), 128, 0, stream, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, rank, n_slices);
-    IB_CHECK_LAUNCH("latent_combine");
-  }
+  if (n_slices > 1) return ib_latent_combine(part_o, part_ml, out, out_dtype, T * heads, rank, n_slices, stream);
   return 0;
 }

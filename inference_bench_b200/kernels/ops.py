@@ -335,6 +335,38 @@ def latent_attention(q_full: torch.Tensor, kv: KvLayerView, positions: torch.Ten
            dtype_code(out.dtype), _ptr(part_o), _ptr(part_ml), T, heads, rank, n_slices, slice_keys, status.data_ptr(), _stream())
 
 
+L.register("ib_latent_attention_mma", [L._p, C.POINTER(L.KvView), L._p, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+
+
+def latent_attention_mma_supports(rank: int, row: int) -> bool:
+    return bool(L.load().ib_latent_attention_mma_supports(int(rank), int(row)))
+
+
+def latent_attention_mma(q_full: torch.Tensor, kv: KvLayerView, positions: torch.Tensor, seg_of_token: torch.Tensor, units: Optional[torch.Tensor], scale: float,
+                         out: torch.Tensor, rank: int, n_slices: int, slice_keys: int, scratch, status: torch.Tensor) -> None:
+    """The same as `latent_attention` on the tensor cores (bfloat16 cache and output). units: None (a CTA per token) or int32 [n, 2] of
+    (first token, tokens): runs of consecutive tokens of one request that share a CTA's 16 query rows (fewer than 16 heads)."""
+    T, heads, D = q_full.shape
+    _check("q_full", q_full, torch.float32)
+    _check("out", out, torch.bfloat16, (T, heads, rank))
+    _check("positions", positions, torch.int32, (T,))
+    _check("seg_of_token", seg_of_token, torch.int32, (T,))
+    view = kv.c_view()
+    if view.head_dim != D:
+        raise L.KernelError(f"latent_attention_mma: queries have {D} values, cache rows {view.head_dim}")
+    n_units = T
+    if units is not None:
+        _check("units", units, torch.int32)
+        n_units = units.shape[0]
+    part_o, part_ml = scratch if scratch is not None else (None, None)
+    if n_slices > 1:
+        if part_o.numel() < T * heads * n_slices * rank or part_ml.numel() < T * heads * n_slices * 2:
+            raise L.KernelError("latent_attention_mma: the scratch for the slices is too small")
+        L.launches += 1
+    L.call("ib_latent_attention_mma", q_full.data_ptr(), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), _ptr(units), n_units, float(scale),
+           out.data_ptr(), _ptr(part_o), _ptr(part_ml), T, heads, rank, n_slices, slice_keys, status.data_ptr(), _stream())
+
+
 # ---------------------------------------------------------------- routed experts (csrc/moe.cu)
 L.register("ib_moe_route", [L._p, L._i, L._ll, L._i, L._i, L._i, L._i, L._i, L._f, L._i, L._p, L._p, L._p])
 L.register("ib_moe_sort", [L._p, L._i, L._i, L._i, L._p, L._p, L._p, L._p, L._p])

@@ -76,10 +76,33 @@ class LatentAttention(base.Mixer):
                 ctas = ctx.n_tokens * -(-self.heads // 8)
                 n = max(1, min(2 * ctx.rt.sm_count // ctas, -(-max_keys // 64)))
                 if n > 1:
-                    per = -(-(-(-max_keys // n)) // 32) * 32
+                    per = -(-(-(-max_keys // n)) // 64) * 64
                     out = (-(-max_keys // per), per)
             ctx.memo[key] = out
         return ctx.memo[key]
+
+    def _units(self, ctx):
+        """For the tensor-core kernel with fewer than 16 heads: runs of consecutive tokens of one request that fill a CTA's 16 query
+        rows, int32 [n, 2] of (first token, tokens) on the device; None when every token is a unit of its own."""
+        per = 16 // self.heads
+        if per <= 1 or ctx.fixed_shape or ctx.max_segment_len == 1:
+            return None
+        key = ("latent units", per)
+        if key not in ctx.memo:
+            runs = []
+            for a, b in zip(ctx.h_seg_start[:-1].tolist(), ctx.h_seg_start[1:].tolist()):
+                runs += [(t, min(per, b - t)) for t in range(a, b, per)]
+            ctx.memo[key] = torch.tensor(runs, dtype=torch.int32).pin_memory().to(ctx.rt.device, non_blocking=True)
+        return ctx.memo[key]
+
+    def _tensor_cores(self, rt) -> bool:
+        how = rt.options.latent_attention
+        if how == "generic" or rt.act_dtype != torch.bfloat16:
+            return False
+        fits = ops.latent_attention_mma_supports(self.kv_rank, self.kv_rank + self.rot_dim)
+        if how == "mma" and not fits:
+            raise ValueError(f"latent_attention = \"mma\" needs a latent and a rotated part that are multiples of 16 (up to 512 and 576 together), got {self.kv_rank} and {self.rot_dim}")
+        return fits
 
     def forward(self, ctx, h, cache):
         rt, T, H, r, rot = ctx.rt, ctx.n_tokens, self.heads, self.kv_rank, self.rot_dim
@@ -98,7 +121,10 @@ class LatentAttention(base.Mixer):
                 ctx.memo[skey] = (rt.empty((T * H * n_slices * r,), torch.float32), rt.empty((T * H * n_slices * 2,), torch.float32))
             scratch = ctx.memo[skey]
         u = rt.empty((T, H, r))
-        ops.latent_attention(q_full, cache, ctx.positions, ctx.seg_of_token, self.scale, u, r, n_slices, slice_keys, scratch, rt.status)
+        if self._tensor_cores(rt):
+            ops.latent_attention_mma(q_full, cache, ctx.positions, ctx.seg_of_token, self._units(ctx), self.scale, u, r, n_slices, slice_keys, scratch, rt.status)
+        else:
+            ops.latent_attention(q_full, cache, ctx.positions, ctx.seg_of_token, self.scale, u, r, n_slices, slice_keys, scratch, rt.status)
         v = rt.empty((T, H, self.vdim))
         ops.gemm_heads(u, self.wuv, v, self.vdim)
         return rt.linear(v.view(T, H * self.vdim), self.wo)

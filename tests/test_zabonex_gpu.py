@@ -81,7 +81,7 @@ def _plain_latent_rows(cache, q, positions, rank, scale):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,rank,rot,page", [(3, 40, 8, 16), (11, 72, 12, 8), (16, 128, 16, 32), (8, 300, 2, 16)])
+@pytest.mark.parametrize("H,rank,rot,page", [(3, 40, 8, 16), (11, 72, 12, 8), (16, 128, 16, 32), (8, 300, 2, 16), (5, 64, 32, 16), (40, 512, 64, 64), (16, 48, 16, 8)])
 def test_latent_attention_kernel_far_keys_page_borders_and_the_causal_edge(rt32, dtype, H, rank, rot, page):
     """One key is made to stand out for one head (its latent and the query share a large entry): the key far back, the keys on both
     sides of a page border, the query's own position (the last key it sees) and the one after it (which it must not see), for a
@@ -111,6 +111,15 @@ def test_latent_attention_kernel_far_keys_page_borders_and_the_causal_edge(rt32,
         ops.latent_attention(_f32(q), view, pos, seg, scale, out, rank, n_slices, slice_keys, scratch, rt32.status)
         err = (out.cpu().double() - want).abs().max().item()
         assert err < tol, f"{n_slices} slices: {err}"
+        if dtype == torch.bfloat16 and ops.latent_attention_mma_supports(rank, rank + rot) and slice_keys % 64 == 0:
+            # the tensor-core kernel rounds the queries to bfloat16 too: compare with the plain sum over those
+            want16 = _plain_latent_rows(cache, q.to(torch.bfloat16).float(), rows, rank, scale)
+            per = max(1, 16 // H)
+            for units in ([None] if per == 1 else [None, torch.tensor([(t, min(per, T - t)) for t in range(0, T, per)], dtype=torch.int32, device=DEV)]):
+                out = torch.full((T, H, rank), 9.0, dtype=dtype, device=DEV)
+                ops.latent_attention_mma(_f32(q), view, pos, seg, units, scale, out, rank, n_slices, slice_keys, scratch, rt32.status)
+                err = (out.cpu().double() - want16).abs().max().item()
+                assert err < 3e-2, f"tensor cores, {n_slices} slices, {'a CTA per token' if units is None else 'tokens sharing a CTA'}: {err}"
     rt32.check_status()
 
 
