@@ -299,15 +299,30 @@ def latent_prepare(qd: torch.Tensor, c_norm_w: Optional[torch.Tensor], eps: floa
            rot, rank, status.data_ptr(), _stream())
 
 
-def gemm_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n: int) -> None:
+L.register("ib_gemm_grouped_mma", [L._p, L._p, L._p, L._p, L._i, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p])
+L.register("ib_gemm_heads_mma", [L._p, L._ll, L._ll, L._p, L._p, L._i, L._ll, L._ll, L._i, L._i, L._i, L._i, L._p])
+
+
+def rows_mma_fits(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel for products on row groups takes these operands: bfloat16, an inner size that is a multiple of 8."""
+    return x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def gemm_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n: int, tensor_cores: bool = False) -> None:
     """out[t, b, :n] = w[b] x[t, b] for every head b: x [T, heads, K] (contiguous), w [heads, N, K], out [T, heads, >= n] whose
-    first n columns of every head are written (the rest stay)."""
+    first n columns of every head are written (the rest stay). tensor_cores: the m16n8k16 kernel (see `rows_mma_fits`)."""
     T, heads, K = x.shape
     _check("x", x)
     _check("w", w, None, (heads, n, K))
     _check("out", out)
     if out.dim() != 3 or out.shape[0] != T or out.shape[1] != heads or out.shape[2] < n:
         raise L.KernelError(f"gemm_heads: out must be [{T}, {heads}, >= {n}], got {tuple(out.shape)}")
+    if tensor_cores:
+        if not rows_mma_fits(x, w):
+            raise L.KernelError("gemm_heads: the tensor-core kernel needs bfloat16 operands with an inner size that is a multiple of 8")
+        L.call("ib_gemm_heads_mma", x.data_ptr(), heads * K, K, w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), heads * out.shape[2], out.shape[2], T, heads, n, K,
+               _stream())
+        return
     L.call("ib_gemm_heads", x.data_ptr(), dtype_code(x.dtype), heads * K, K, w.data_ptr(), dtype_code(w.dtype), out.data_ptr(), dtype_code(out.dtype),
            heads * out.shape[2], out.shape[2], T, heads, n, K, _stream())
 
@@ -394,7 +409,7 @@ def moe_sort(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, tile_star
 
 
 def gemm_grouped(x: torch.Tensor, src_row: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, tile_start: torch.Tensor,
-                 gated: bool) -> None:
+                 gated: bool, tensor_cores: bool = False) -> None:
     """out[r] = w[e(r)] x[src_row[r] or r] for the regrouped rows r (expert e's rows are offsets[e]..offsets[e+1]); w [E, N or 2N, K]; with
     `gated`, w holds gate rows then up rows and out = silu(gate) * up."""
     R, N = out.shape
@@ -406,6 +421,12 @@ def gemm_grouped(x: torch.Tensor, src_row: Optional[torch.Tensor], w: torch.Tens
     _check("out", out)
     if src_row is not None:
         _check("src_row", src_row, torch.int32, (R,))
+    if tensor_cores:
+        if not rows_mma_fits(x, w):
+            raise L.KernelError("gemm_grouped: the tensor-core kernel needs bfloat16 operands with an inner size that is a multiple of 8")
+        L.call("ib_gemm_grouped_mma", x.data_ptr(), _ptr(src_row), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), offsets.data_ptr(), tile_start.data_ptr(), R, E,
+               N, K, 1 if gated else 0, _stream())
+        return
     L.call("ib_gemm_grouped", x.data_ptr(), dtype_code(x.dtype), _ptr(src_row), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(), dtype_code(out.dtype),
            offsets.data_ptr(), tile_start.data_ptr(), R, E, N, K, 1 if gated else 0, _stream())
 

@@ -62,9 +62,10 @@ class RoutedExperts(base.FeedForward):
         row_of_pair, token_of_row = rt.empty((R,), torch.int32), rt.empty((R,), torch.int32)
         ops.moe_sort(idx, E, offsets, tile_start, row_of_pair, token_of_row)
         act = rt.empty((R, self.expert_ff))
-        ops.gemm_grouped(h, token_of_row, self.w_gu, act, offsets, tile_start, gated=True)
+        tc = rt.options.expert_gemm != "simt"
+        ops.gemm_grouped(h, token_of_row, self.w_gu, act, offsets, tile_start, gated=True, tensor_cores=tc and ops.rows_mma_fits(h, self.w_gu))
         y = rt.empty((R, self.hidden), torch.float32)
-        ops.gemm_grouped(act, None, self.w_d, y, offsets, tile_start, gated=False)
+        ops.gemm_grouped(act, None, self.w_d, y, offsets, tile_start, gated=False, tensor_cores=tc and ops.rows_mma_fits(act, self.w_d))
         shared = rt.linear(rt.gate_up_act(h, self.shared_gu), self.shared_d) if self.shared_ff else None
         out = rt.empty((1, T, self.hidden), torch.float32)
         ops.moe_combine(y, row_of_pair, wt, shared, out[0])

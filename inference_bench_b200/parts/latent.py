@@ -112,7 +112,8 @@ class LatentAttention(base.Mixer):
         q_full = rt.empty((T, H, r + rot), torch.float32)
         ops.latent_prepare(qd, self.c_norm, self.norm_eps, cos, sin, ctx.positions, ctx.seg_of_token, q_nope, q_full, cache, H, self.dim, rot, r,
                            self.own_kv, rt.status)
-        ops.gemm_heads(q_nope, self.wuk_t, q_full, r)
+        tc = rt.options.expert_gemm != "simt"
+        ops.gemm_heads(q_nope, self.wuk_t, q_full, r, tensor_cores=tc and ops.rows_mma_fits(q_nope, self.wuk_t))
         n_slices, slice_keys = self._slices(ctx, cache.c_view())
         scratch = None
         if n_slices > 1:
@@ -126,5 +127,5 @@ class LatentAttention(base.Mixer):
         else:
             ops.latent_attention(q_full, cache, ctx.positions, ctx.seg_of_token, self.scale, u, r, n_slices, slice_keys, scratch, rt.status)
         v = rt.empty((T, H, self.vdim))
-        ops.gemm_heads(u, self.wuv, v, self.vdim)
+        ops.gemm_heads(u, self.wuv, v, self.vdim, tensor_cores=tc and ops.rows_mma_fits(u, self.wuv))
         return rt.linear(v.view(T, H * self.vdim), self.wo)

@@ -165,13 +165,20 @@ def test_latent_prepare_writes_queries_and_the_cache_row(rt32, H, dim, rot, rank
 def test_per_head_products(rt32):
     from inference_bench_b200.kernels import ops
     g = torch.Generator().manual_seed(3)
-    for T, H, N, K, pad in ((1, 3, 40, 24, 8), (70, 11, 10, 72, 0), (130, 2, 65, 17, 3)):
+    for T, H, N, K, pad in ((1, 3, 40, 24, 8), (70, 11, 10, 72, 0), (130, 2, 65, 17, 3), (200, 4, 130, 136, 6)):
         x, w = torch.randn((T, H, K), generator=g), torch.randn((H, N, K), generator=g)
         out = torch.full((T, H, N + pad), 7.0, device=DEV)
         ops.gemm_heads(_f32(x), _f32(w), out, N)
         want = torch.einsum("thk,hnk->thn", x.double(), w.double())
         assert torch.allclose(out.cpu().double()[..., :N], want, atol=1e-4)
         assert (out[..., N:] == 7.0).all()
+        if K % 8 == 0:   # bfloat16 operands on the tensor cores, float32 and bfloat16 outputs
+            xb, wb = x.to(DEV, torch.bfloat16), w.to(DEV, torch.bfloat16)
+            want16 = torch.einsum("thk,hnk->thn", xb.cpu().double(), wb.cpu().double())
+            for dt, atol, rtol in ((torch.float32, 1e-4, 1e-5), (torch.bfloat16, 1e-2, 1e-2)):
+                out = torch.full((T, H, N + pad), 7.0, device=DEV, dtype=dt)
+                ops.gemm_heads(xb, wb, out, N, tensor_cores=True)
+                assert torch.allclose(out.cpu().double()[..., :N], want16, atol=atol, rtol=rtol) and (out[..., N:] == 7.0).all()
 
 
 @pytest.mark.parametrize("E,groups,keep,top,scale", [(12, 4, 2, 3, 2.0), (64, 8, 3, 6, 0.5), (5, 1, 1, 1, 1.0), (6, 3, 1, 2, 1.0), (40, 40, 7, 7, 1.0)])
@@ -200,7 +207,7 @@ def test_router_choice(rt32, E, groups, keep, top, scale):
 
 
 @pytest.mark.parametrize("T", [1, 2, 9, 150])
-@pytest.mark.parametrize("E,top,W,F", [(5, 1, 80, 40), (16, 4, 132, 36), (3, 3, 64, 70)])
+@pytest.mark.parametrize("E,top,W,F", [(5, 1, 80, 40), (16, 4, 132, 36), (3, 3, 64, 70), (7, 2, 200, 136)])
 def test_experts_on_regrouped_rows(rt32, T, E, top, W, F):
     """Regrouping by expert, the experts' two products and the weighted sum, against the plain loop over tokens; the rows an expert
     gets span several tiles for the largest T and some experts get none for the smallest."""
@@ -231,6 +238,18 @@ def test_experts_on_regrouped_rows(rt32, T, E, top, W, F):
     ops.gemm_grouped(act, None, _f32(w_d), y, offsets, tile_start, gated=False)
     ops.moe_combine(y, row_of_pair, _f32(wt), _f32(base), out)
     assert torch.allclose(out.cpu().double(), want, atol=1e-4)
+    if W % 8 == 0 and F % 8 == 0:   # the same on the tensor cores with bfloat16 operands (the activation handed on in bfloat16)
+        hb, gub, db = h.to(DEV, torch.bfloat16), w_gu.to(DEV, torch.bfloat16), w_d.to(DEV, torch.bfloat16)
+        want16 = base.double().sum(0)
+        for t in range(T):
+            for k in range(top):
+                e = int(idx[t, k])
+                want16[t] += wt[t, k].double() * P.gated_ff(hb[t:t + 1].cpu().double(), gub[e, :F].cpu().double(), gub[e, F:].cpu().double(), db[e].cpu().double(), P.bf16)[0]
+        act16 = torch.empty((R, F), device=DEV, dtype=torch.bfloat16)
+        ops.gemm_grouped(hb, token_of_row, gub, act16, offsets, tile_start, gated=True, tensor_cores=True)
+        ops.gemm_grouped(act16, None, db, y, offsets, tile_start, gated=False, tensor_cores=True)
+        ops.moe_combine(y, row_of_pair, _f32(wt), _f32(base), out)
+        assert torch.allclose(out.cpu().double(), want16, atol=2e-3)
 
 
 # ------------------------------------------------------------------------------------------ whole models
