@@ -410,6 +410,168 @@ def run_ours(args) -> dict:
     }
 
 
+# ---------------------------------------------------------------------------------------------- another design beside the closest Qwen3
+# Layer sizes that resemble published latent-attention models with routed experts (a 16-head one with 64 experts, and a small one),
+# and the Qwen3 shape of equal width, heads and active feed-forward size. Layers alternate: one that keeps its own latent, one that
+# reads the layer before's; the first feed-forward is dense, the rest are routed.
+DESIGN_SIZES = {
+    "small": dict(width=1024, heads=8, dim=64, rot=32, vdim=64, rank=256, dense_ff=4096, experts=16, top=2, expert_ff=1024, shared_ff=1024, groups=(4, 2), vocab=32768),
+    "lite": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, dense_ff=10944, experts=64, top=6, expert_ff=1408, shared_ff=2816, groups=(8, 4), vocab=32768),
+}
+DESIGN_KINDS = {   # kinds of kernel by the library entry points that launch them
+    "zabonex": {"attention": ["ib_latent_attention", "ib_latent_attention_mma"], "experts": ["ib_gemm_grouped", "ib_gemm_grouped_mma"],
+                "heads": ["ib_gemm_heads", "ib_gemm_heads_mma"], "route": ["ib_moe_route", "ib_moe_sort", "ib_moe_combine"],
+                "norm": ["ib_norm_residual", "ib_latent_prepare", "ib_cast_rows"], "gemm": LEAVE_OUT["gemm"]},
+    "qwen3": {"attention": LEAVE_OUT["attention"], "norm": LEAVE_OUT["norm"] + LEAVE_OUT["qk"], "gemm": LEAVE_OUT["gemm"] + LEAVE_OUT["qkv"]},
+}
+
+
+def kernel_times(engine, entries) -> dict:
+    """Milliseconds per library entry point in one step run outside a graph: every call stands between two CUDA events, and a
+    long idle kernel goes first so that the whole step is queued before its first kernel starts (the events then measure the
+    kernels, not the host). A kernel timed this way stands alone: it overlaps nothing of its neighbours."""
+    import torch
+    from inference_bench_b200.kernels import lib as L
+    real, log = L.call, []
+
+    def timed(name, *a):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        real(name, *a)
+        e1.record()
+        log.append((name, e0, e1))
+
+    torch.cuda.synchronize()
+    torch.cuda._sleep(40_000_000)
+    L.call = timed
+    try:
+        engine.runner.step(entries, check=False)
+    finally:
+        L.call = real
+    torch.cuda.synchronize()
+    out: dict = {}
+    for name, e0, e1 in log:
+        t = out.setdefault(name, [0.0, 0])
+        t[0] += e0.elapsed_time(e1)
+        t[1] += 1
+    return out
+
+
+def zabonex_config(z: dict, layers: int) -> dict:
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["rank"], "scale": (z["dim"] + z["rot"]) ** -0.5,
+             "rot": {"base": 10000.0, "dims": z["rot"]}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["shared_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0, "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    ls = []
+    for i in range(layers):
+        m = dict(mixer, kv_from=i - 1) if i % 2 else dict(mixer)
+        ls.append({"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": z["dense_ff"]} if i == 0 else moe})
+    return {"architecture": "Zabonex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.7, "layers": ls}
+
+
+def qwen3_like(z: dict, layers: int) -> dict:
+    return dict(QWEN3_8B, vocab_size=z["vocab"], hidden_size=z["width"], num_hidden_layers=layers, num_attention_heads=z["heads"],
+                num_key_value_heads=max(1, z["heads"] // 4), head_dim=128 if z["dim"] + z["rot"] > 96 else 64, intermediate_size=z["top"] * z["expert_ff"] + z["shared_ff"])
+
+
+def design_work(z: dict, layers: int, T: int, ctx: int, batch: int) -> dict:
+    """Algorithmic FLOPs and bytes of the new design's own kinds of kernel, for a prefill of T tokens and for a decode step of `batch`
+    requests at `ctx` tokens of context (per step, all layers)."""
+    H, D, r = z["heads"], z["rank"] + z["rot"], z["rank"]
+    moe_layers = layers - 1
+    pairs = T * (T + 1) / 2
+    return {
+        "prefill": {"attention": {"flops": layers * 2.0 * H * pairs * (D + r)},
+                    "experts": {"flops": moe_layers * 2.0 * T * z["top"] * 3 * z["expert_ff"] * z["width"]},
+                    "heads": {"flops": layers * 2.0 * T * H * r * (z["dim"] + z["vdim"])}},
+        "decode": {"attention": {"flops": layers * 2.0 * H * batch * ctx * (D + r), "bytes": layers * 2.0 * batch * ctx * D},
+                   "experts": {"flops": moe_layers * 2.0 * batch * z["top"] * 3 * z["expert_ff"] * z["width"],
+                               "bytes": moe_layers * 2.0 * min(batch * z["top"], z["experts"]) * 3 * z["expert_ff"] * z["width"]},
+                   "heads": {"flops": layers * 2.0 * batch * H * r * (z["dim"] + z["vdim"]), "bytes": layers * 2.0 * H * r * (z["dim"] + z["vdim"])}},
+    }
+
+
+def qwen3_work(cfg: dict, layers: int, T: int, ctx: int, batch: int) -> dict:
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    return {"prefill": {"attention": {"flops": layers * 4.0 * (T * (T + 1) / 2) * q}},
+            "decode": {"attention": {"flops": layers * 4.0 * batch * ctx * q, "bytes": batch * ctx * kv_bytes_per_token(cfg, layers)}}}
+
+
+def run_design(args) -> dict:
+    """Prefill (one portion of 2,048 tokens) and decode (batch 1, 8, 64 at 2,048 tokens of context) of Zabonex at sizes that resemble
+    real models, beside the Qwen3 shape of equal width, heads and active feed-forward; and every kind of kernel of one prefill step
+    and one decode step of 8 requests timed alone with CUDA events, with how far that is from the kind's roofline (the slower of
+    its FLOPs at the measured matrix-product peak and its bytes at the measured copy bandwidth)."""
+    import gc
+
+    import torch
+    from inference_bench_b200 import Engine
+    from inference_bench_b200.engine.step import StepEntry
+    pk, pk_src = peaks()
+    layers = args.layers or 4
+    steps, warmup = min(args.steps, 32), max(args.warmup, 3)
+    out = {"design": "zabonex", "layers": layers, "peaks": pk_src, "sizes": {}}
+    for name in (args.size.split(",") if args.size else list(DESIGN_SIZES)):
+        z = DESIGN_SIZES[name]
+        report = {}
+        for arch, cfg in (("zabonex", zabonex_config(z, layers)), ("qwen3", qwen3_like(z, layers))):
+            engine = Engine(cfg, dtype="bfloat16", max_ctx=CONTEXT, page_size=PAGE_ENGINE, num_pages=64 * (CONTEXT // PAGE_ENGINE) + 64, max_num_seqs=64,
+                            max_batched_tokens=8192, prefill_chunk=PROMPT, random_weights_seed=0)
+            vocab = engine.decoder.plan.vocab_size
+            if arch == "zabonex":
+                work = design_work(z, layers, PROMPT, PROMPT, 8)
+                lin = layers * (z["heads"] * (z["dim"] + z["rot"]) + z["heads"] * z["vdim"]) * z["width"] + (layers + 1) // 2 * (z["rank"] + z["rot"]) * z["width"] + \
+                    3 * z["dense_ff"] * z["width"] + (layers - 1) * (3 * z["shared_ff"] + z["experts"]) * z["width"] + vocab * z["width"]
+            else:
+                work = qwen3_work(cfg, layers, PROMPT, PROMPT, 8)
+                lin = weight_bytes(cfg, layers) // 2
+            work["prefill"]["gemm"] = {"flops": 2.0 * PROMPT * (lin - vocab * z["width"]) + 2.0 * vocab * z["width"]}
+            work["decode"]["gemm"] = {"flops": 2.0 * 8 * lin, "bytes": 2.0 * lin}
+            r = {"prefill_ms": measure_prefill(engine, 3, 2)}
+            r["prefill_tok_s"] = PROMPT * 1e3 / r["prefill_ms"]
+            for b in (1, 8, 64):
+                ms, launches = measure_decode_device(engine, b, steps, warmup)
+                r[f"decode_b{b}_ms"], r[f"decode_b{b}_tok_s"] = ms, b * 1e3 / ms
+                if b == 8:
+                    r["launches_per_decode_step"] = launches
+            # kernels alone: the prefill of one request, then one step of 8 decoded tokens at 2,048 tokens of context
+            ids = [("k", i) for i in range(8)]
+            for i, rid in enumerate(ids):
+                engine.cache.admit(rid)
+                e = [StepEntry(rid, _prompt(4000 + i, PROMPT, vocab), [PROMPT - 1])]
+                if i < 7:
+                    engine.runner.step(e, check=False)
+                else:
+                    times_p = kernel_times(engine, e)
+            kernel_times(engine, [StepEntry(rid, [1 + i], [0]) for i, rid in enumerate(ids)])   # once for lazy set-up
+            times_d = kernel_times(engine, [StepEntry(rid, [9 + i], [0]) for i, rid in enumerate(ids)])
+            for rid in ids:
+                engine.cache.release(rid)
+            engine.rt.check_status()
+            kinds = {}
+            for kind, names in DESIGN_KINDS[arch].items():
+                k = {}
+                for phase, times in (("prefill", times_p), ("decode", times_d)):
+                    ms, n = sum(times[x][0] for x in names if x in times), sum(times[x][1] for x in names if x in times)
+                    if not n:
+                        continue
+                    k[f"{phase}_ms"], k[f"{phase}_calls"] = ms, n
+                    w = work[phase].get(kind)
+                    if w:
+                        floor = max(w["flops"] / (pk["bf16_tflops"] * 1e12), w.get("bytes", 0.0) / (pk["hbm_gbs"] * 1e9)) * 1e3
+                        k[f"{phase}_roofline_frac"] = floor / ms
+                if k:
+                    kinds[kind] = k
+            r["kinds"] = kinds
+            r["kernels_alone_ms"] = {"prefill": sum(t[0] for t in times_p.values()), "decode_b8": sum(t[0] for t in times_d.values())}
+            report[arch] = r
+            del engine
+            gc.collect()
+            torch.cuda.empty_cache()
+        out["sizes"][name] = report
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -425,7 +587,12 @@ def main() -> int:
     ap.add_argument("--leave-out", default="", help="with --only decode or prefill: also time the step without each of these kinds of kernel (comma separated; "
                     "a+b leaves both out): " + ", ".join(sorted(LEAVE_OUT)))
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "mixed"], help="run one part alone (for profiling); prints a short report")
+    ap.add_argument("--design", default="", choices=["", "zabonex"], help="measure another design beside the Qwen3 shape of equal size instead of the benchmark (prints its own report)")
+    ap.add_argument("--size", default="", help="with --design: which of its sizes (comma separated; default all): " + ", ".join(DESIGN_SIZES))
     args = ap.parse_args()
+    if args.design:
+        print(json.dumps(run_design(args)))
+        return 0
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no setup.py/pyproject.toml): pip cannot install it and no Rust toolchain is present"}))
         return 0

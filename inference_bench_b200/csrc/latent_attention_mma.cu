@@ -2,9 +2,9 @@
 // (a head's query [Wuk^T q_n | q_r] against the cached rows [c | kr], softmax in float32, weighted sum of the latents c),
 // for row sizes that are multiples of 16.
 //
-// A CTA of four warps owns 16 query rows: the heads of one token (blocks of 16 heads when there are more; several consecutive
-// tokens of one request when there are fewer than 16 heads), and walks the keys they see in tiles of 64, which all its rows
-// share: a cached row is read once for all heads. Per tile:
+// A CTA of four warps owns 16, 32 or 64 query rows: the heads of one token (blocks of heads when there are more; several consecutive
+// tokens of one request when a prompt portion has them), and walks the keys they see in tiles of 64, which all its rows
+// share: a cached row is read once for all of them (with 16 rows the kernel is bound by the key tiles' way from L2). Per tile:
 //   S = Q K^T   warp w takes keys 16w..16w+15 over the whole row (m16n8k16, float32 accumulators), scales and masks them,
 //               and the four warps exchange row maxima and row sums through shared memory;
 //   P           float32 weights exp(s - m), rounded to bfloat16 only as the operand of the second product; the sums l use
@@ -13,33 +13,35 @@
 // Key tiles are copied with 16-byte cp.async through the block table into two swizzled buffers (the next tile arrives while
 // this one is used); rows past the last visible key are zero-filled. With slices (steps of single decoded tokens), a CTA
 // takes one slice of the keys and writes unnormalised partial results that latent_combine merges.
+#include <type_traits>
+
 #include "kv_view.cuh"
 #include "mma_tiles.cuh"
 
 namespace {
 
-constexpr int kRows = 16;    // query rows of a CTA
 constexpr int kKeys = 64;    // keys of a tile
 constexpr int kWarps = 4;
 
-// NCH: 16-value chunks of the latent a warp owns at most (rank <= 64 * NCH).
-template <int NCH>
+// NCH: 16-value chunks of the latent a warp owns at most (rank <= 64 * NCH). MT: 16-row tiles of queries a CTA holds.
+template <int NCH, int MT>
 __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const float* __restrict__ q, IbKvView kv, const int* __restrict__ positions,
                                                                            const int* __restrict__ seg_of_token, const int2* __restrict__ units, float scale,
                                                                            __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                                                                            int H, int rank, int D, int n_slices, int slice_keys, unsigned* __restrict__ status) {
+  constexpr int R = 16 * MT;                                 // query rows of the CTA
   extern __shared__ __align__(128) unsigned char smem[];
   const int blocks = (D + 63) / 64;                          // 64-value blocks of a row
   const uint32_t k_bytes = (uint32_t)blocks * kKeys * 128;   // one key tile
   const uint32_t s_k = mt::smem_u32(smem);                   // two key tiles
-  const uint32_t s_q = s_k + 2 * k_bytes;                    // [16][D]
-  const uint32_t s_p = s_q + (uint32_t)blocks * kRows * 128; // [16][64]
-  float* wmax = (float*)(smem + 2 * k_bytes + (size_t)blocks * kRows * 128 + kRows * 128);   // [4][16]
-  float* wsum = wmax + kWarps * kRows;                                                       // [4][16]
+  const uint32_t s_q = s_k + 2 * k_bytes;                    // [R][D]
+  const uint32_t s_p = s_q + (uint32_t)blocks * R * 128;     // [R][64]
+  float* wmax = (float*)(smem + 2 * k_bytes + (size_t)blocks * R * 128 + R * 128);   // [4][R]
+  float* wsum = wmax + kWarps * R;                                                   // [4][R]
   ib::pdl_launch_dependents();
   ib::pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-  const int hpc = H < kRows ? H : kRows;                     // heads a CTA covers
+  const int hpc = H < R ? H : R;                             // heads a CTA covers
   const int h0 = blockIdx.x * hpc;
   int tok0 = blockIdx.y, ntok = 1;
   if (units) {
@@ -51,18 +53,20 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
   const int last_pos = positions[tok0 + ntok - 1];
   const int lo = slice * slice_keys;
   const int hi = min(last_pos, lo + slice_keys - 1);
-  // the two rows this thread sees in an accumulator: g and g + 8
-  int row_pos[2], row_tok[2], row_head[2];
+  // the rows this thread sees in its accumulators: g + 8 e of every 16-row tile
+  int row_pos[MT][2], row_tok[MT][2], row_head[MT][2];
 #pragma unroll
-  for (int e = 0; e < 2; e++) {
-    const int r = g + 8 * e, tl = r / hpc, hh = r - tl * hpc;
-    const bool valid = tl < ntok && h0 + hh < H;
-    row_tok[e] = valid ? tok0 + tl : -1;
-    row_head[e] = h0 + hh;
-    row_pos[e] = valid ? positions[tok0 + tl] : -1;
-  }
-  // queries -> bfloat16, swizzled [16][D]
-  for (int idx = tid; idx < kRows * (D / 8); idx += kWarps * 32) {
+  for (int a = 0; a < MT; a++)
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      const int r = 16 * a + g + 8 * e, tl = r / hpc, hh = r - tl * hpc;
+      const bool valid = tl < ntok && h0 + hh < H;
+      row_tok[a][e] = valid ? tok0 + tl : -1;
+      row_head[a][e] = h0 + hh;
+      row_pos[a][e] = valid ? positions[tok0 + tl] : -1;
+    }
+  // queries -> bfloat16, swizzled [R][D]
+  for (int idx = tid; idx < R * (D / 8); idx += kWarps * 32) {
     const int r = idx / (D / 8), c = idx - r * (D / 8);
     const int tl = r / hpc, hh = r - tl * hpc;
     uint32_t w[4] = {0u, 0u, 0u, 0u};
@@ -71,7 +75,7 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
       const float4 a = *(const float4*)src, b = *(const float4*)(src + 4);
       w[0] = mt::pack_bf16(a.x, a.y), w[1] = mt::pack_bf16(a.z, a.w), w[2] = mt::pack_bf16(b.x, b.y), w[3] = mt::pack_bf16(b.z, b.w);
     }
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(s_q + mt::tile_offset<64, kRows>(r, c)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(s_q + mt::tile_offset<64, R>(r, c)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
   }
   const __nv_bfloat16* base = (const __nv_bfloat16*)kv.base;
   // eight threads copy one row's 128-byte pieces; sixteen rows a pass
@@ -93,14 +97,19 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
     }
     mt::cp_async_commit();
   };
-  float o[NCH][2][4];
+  float o[MT][NCH][2][4];
+  float m[MT][2], l[MT][2];
 #pragma unroll
-  for (int i = 0; i < NCH; i++)
+  for (int a = 0; a < MT; a++) {
+    m[a][0] = m[a][1] = -INFINITY;
+    l[a][0] = l[a][1] = 0.f;
 #pragma unroll
-    for (int n = 0; n < 2; n++)
+    for (int i = 0; i < NCH; i++)
 #pragma unroll
-      for (int e = 0; e < 4; e++) o[i][n][e] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+      for (int n = 0; n < 2; n++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[a][i][n][e] = 0.f;
+  }
   const int n_tiles = hi >= lo ? (hi - lo) / kKeys + 1 : 0;
   if (n_tiles > 0) issue_tile(lo, 0);
   for (int j = 0; j < n_tiles; j++) {
@@ -109,123 +118,155 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
     __syncthreads();                                       // tile j is here; everybody is done with tile j - 1 and with P
     if (j + 1 < n_tiles) issue_tile(k0 + kKeys, buf ^ 1);
     const uint32_t kt = s_k + buf * k_bytes;
-    // ---- S: this warp's 16 keys
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // ---- S: this warp's 16 keys, every row tile
+    float s[MT][2][4];
+#pragma unroll
+    for (int a = 0; a < MT; a++)
+#pragma unroll
+      for (int n = 0; n < 2; n++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) s[a][n][e] = 0.f;
+#pragma unroll 2
     for (int kk = 0; kk < D / 16; kk++) {
-      uint32_t a[4], r[4];
-      mt::load_a_frag<64, kRows>(s_q, 0, kk, lane, a);
+      uint32_t r[4];
       mt::load_k_frag<64, kKeys>(kt, 16 * warp, kk, lane, r);
-      mt::mma_16816(s[0], a, r[0], r[1]);
-      mt::mma_16816(s[1], a, r[2], r[3]);
-    }
-    float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int n = 0; n < 2; n++)
-#pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const int key = k0 + 16 * warp + 8 * n + 2 * t4 + (e & 1), rr = e >> 1;
-        const float v = (key <= hi && key <= row_pos[rr]) ? s[n][e] * scale : -INFINITY;
-        s[n][e] = v;
-        mx[rr] = fmaxf(mx[rr], v);
+      for (int a = 0; a < MT; a++) {
+        uint32_t fa[4];
+        mt::load_a_frag<64, R>(s_q, 16 * a, kk, lane, fa);
+        mt::mma_16816(s[a][0], fa, r[0], r[1]);
+        mt::mma_16816(s[a][1], fa, r[2], r[3]);
       }
+    }
 #pragma unroll
-    for (int rr = 0; rr < 2; rr++) {
-      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
-      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
-      if (t4 == 0) wmax[warp * kRows + g + 8 * rr] = mx[rr];
+    for (int a = 0; a < MT; a++) {
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < 2; n++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const int key = k0 + 16 * warp + 8 * n + 2 * t4 + (e & 1), rr = e >> 1;
+          const float v = (key <= hi && key <= row_pos[a][rr]) ? s[a][n][e] * scale : -INFINITY;
+          s[a][n][e] = v;
+          mx[rr] = fmaxf(mx[rr], v);
+        }
+#pragma unroll
+      for (int rr = 0; rr < 2; rr++) {
+        mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+        mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+        if (t4 == 0) wmax[warp * R + 16 * a + g + 8 * rr] = mx[rr];
+      }
     }
     __syncthreads();
-    float corr[2], sum[2];
+    float corr[MT][2];
 #pragma unroll
-    for (int rr = 0; rr < 2; rr++) {
-      const int r = g + 8 * rr;
-      const float mt_ = fmaxf(fmaxf(wmax[r], wmax[kRows + r]), fmaxf(wmax[2 * kRows + r], wmax[3 * kRows + r]));
-      const float m_new = fmaxf(m[rr], mt_);
-      corr[rr] = m_new == -INFINITY ? 1.f : __expf(m[rr] - m_new);
-      m[rr] = m_new;
-      sum[rr] = 0.f;
-    }
+    for (int a = 0; a < MT; a++) {
+      float sum[2];
 #pragma unroll
-    for (int n = 0; n < 2; n++) {
-      float p[4];
-#pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const int rr = e >> 1;
-        p[e] = s[n][e] == -INFINITY ? 0.f : __expf(s[n][e] - m[rr]);
-        sum[rr] += p[e];
+      for (int rr = 0; rr < 2; rr++) {
+        const int r = 16 * a + g + 8 * rr;
+        const float mt_ = fmaxf(fmaxf(wmax[r], wmax[R + r]), fmaxf(wmax[2 * R + r], wmax[3 * R + r]));
+        const float m_new = fmaxf(m[a][rr], mt_);
+        corr[a][rr] = m_new == -INFINITY ? 1.f : __expf(m[a][rr] - m_new);
+        m[a][rr] = m_new;
+        sum[rr] = 0.f;
       }
-      const int chunk = 2 * warp + n;   // 8 keys a chunk
-      asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_p + mt::tile_offset<64, kRows>(g, chunk) + 4 * t4), "r"(mt::pack_bf16(p[0], p[1])) : "memory");
-      asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_p + mt::tile_offset<64, kRows>(g + 8, chunk) + 4 * t4), "r"(mt::pack_bf16(p[2], p[3])) : "memory");
-    }
-#pragma unroll
-    for (int rr = 0; rr < 2; rr++) {
-      sum[rr] += __shfl_xor_sync(0xffffffffu, sum[rr], 1);
-      sum[rr] += __shfl_xor_sync(0xffffffffu, sum[rr], 2);
-      if (t4 == 0) wsum[warp * kRows + g + 8 * rr] = sum[rr];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int rr = 0; rr < 2; rr++) {
-      const int r = g + 8 * rr;
-      l[rr] = l[rr] * corr[rr] + ((wsum[r] + wsum[kRows + r]) + (wsum[2 * kRows + r] + wsum[3 * kRows + r]));
-    }
-#pragma unroll
-    for (int i = 0; i < NCH; i++)
 #pragma unroll
       for (int n = 0; n < 2; n++) {
-        o[i][n][0] *= corr[0], o[i][n][1] *= corr[0];
-        o[i][n][2] *= corr[1], o[i][n][3] *= corr[1];
+        float p[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const int rr = e >> 1;
+          p[e] = s[a][n][e] == -INFINITY ? 0.f : __expf(s[a][n][e] - m[a][rr]);
+          sum[rr] += p[e];
+        }
+        const int chunk = 2 * warp + n;   // 8 keys a chunk
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_p + mt::tile_offset<64, R>(16 * a + g, chunk) + 4 * t4), "r"(mt::pack_bf16(p[0], p[1])) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_p + mt::tile_offset<64, R>(16 * a + g + 8, chunk) + 4 * t4), "r"(mt::pack_bf16(p[2], p[3])) : "memory");
       }
+#pragma unroll
+      for (int rr = 0; rr < 2; rr++) {
+        sum[rr] += __shfl_xor_sync(0xffffffffu, sum[rr], 1);
+        sum[rr] += __shfl_xor_sync(0xffffffffu, sum[rr], 2);
+        if (t4 == 0) wsum[warp * R + 16 * a + g + 8 * rr] = sum[rr];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int a = 0; a < MT; a++) {
+#pragma unroll
+      for (int rr = 0; rr < 2; rr++) {
+        const int r = 16 * a + g + 8 * rr;
+        l[a][rr] = l[a][rr] * corr[a][rr] + ((wsum[r] + wsum[R + r]) + (wsum[2 * R + r] + wsum[3 * R + r]));
+      }
+#pragma unroll
+      for (int i = 0; i < NCH; i++)
+#pragma unroll
+        for (int n = 0; n < 2; n++) {
+          o[a][i][n][0] *= corr[a][0], o[a][i][n][1] *= corr[a][0];
+          o[a][i][n][2] *= corr[a][1], o[a][i][n][3] *= corr[a][1];
+        }
+    }
     // ---- O += P C: this warp's chunks of the latent
 #pragma unroll
     for (int ks = 0; ks < kKeys / 16; ks++) {
-      uint32_t a[4];
-      mt::load_a_frag<64, kRows>(s_p, 0, ks, lane, a);
+      uint32_t fa[MT][4];
+#pragma unroll
+      for (int a = 0; a < MT; a++) mt::load_a_frag<64, R>(s_p, 16 * a, ks, lane, fa[a]);
 #pragma unroll
       for (int i = 0; i < NCH; i++) {
         const int dp = warp + kWarps * i;
         if (dp * 16 < rank) {
           uint32_t r[4];
           mt::load_v_frag<64, kKeys>(kt, 16 * ks, dp, lane, r);
-          mt::mma_16816(o[i][0], a, r[0], r[1]);
-          mt::mma_16816(o[i][1], a, r[2], r[3]);
+#pragma unroll
+          for (int a = 0; a < MT; a++) {
+            mt::mma_16816(o[a][i][0], fa[a], r[0], r[1]);
+            mt::mma_16816(o[a][i][1], fa[a], r[2], r[3]);
+          }
         }
       }
     }
   }
   // ---- out
 #pragma unroll
-  for (int rr = 0; rr < 2; rr++) {
-    if (row_tok[rr] < 0) continue;
-    const size_t th = (size_t)row_tok[rr] * H + row_head[rr];
-    if (n_slices == 1) {
-      const float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
-      __nv_bfloat16* dst = out + th * rank;
+  for (int a = 0; a < MT; a++)
 #pragma unroll
-      for (int i = 0; i < NCH; i++) {
-        const int dp = warp + kWarps * i;
-        if (dp * 16 >= rank) continue;
+    for (int rr = 0; rr < 2; rr++) {
+      if (row_tok[a][rr] < 0) continue;
+      const size_t th = (size_t)row_tok[a][rr] * H + row_head[a][rr];
+      if (n_slices == 1) {
+        const float inv = l[a][rr] > 0.f ? 1.f / l[a][rr] : 0.f;
+        __nv_bfloat16* dst = out + th * rank;
 #pragma unroll
-        for (int n = 0; n < 2; n++)
-          *(uint32_t*)(dst + dp * 16 + 8 * n + 2 * t4) = mt::pack_bf16(o[i][n][2 * rr] * inv, o[i][n][2 * rr + 1] * inv);
-      }
-    } else {
-      const size_t unit = th * n_slices + slice;
-      float* dst = part_o + unit * rank;
+        for (int i = 0; i < NCH; i++) {
+          const int dp = warp + kWarps * i;
+          if (dp * 16 >= rank) continue;
 #pragma unroll
-      for (int i = 0; i < NCH; i++) {
-        const int dp = warp + kWarps * i;
-        if (dp * 16 >= rank) continue;
+          for (int n = 0; n < 2; n++)
+            *(uint32_t*)(dst + dp * 16 + 8 * n + 2 * t4) = mt::pack_bf16(o[a][i][n][2 * rr] * inv, o[a][i][n][2 * rr + 1] * inv);
+        }
+      } else {
+        const size_t unit = th * n_slices + slice;
+        float* dst = part_o + unit * rank;
 #pragma unroll
-        for (int n = 0; n < 2; n++) *(float2*)(dst + dp * 16 + 8 * n + 2 * t4) = make_float2(o[i][n][2 * rr], o[i][n][2 * rr + 1]);
-      }
-      if (warp == 0 && t4 == 0) {
-        part_ml[2 * unit] = m[rr];
-        part_ml[2 * unit + 1] = l[rr];
+        for (int i = 0; i < NCH; i++) {
+          const int dp = warp + kWarps * i;
+          if (dp * 16 >= rank) continue;
+#pragma unroll
+          for (int n = 0; n < 2; n++) *(float2*)(dst + dp * 16 + 8 * n + 2 * t4) = make_float2(o[a][i][n][2 * rr], o[a][i][n][2 * rr + 1]);
+        }
+        if (warp == 0 && t4 == 0) {
+          part_ml[2 * unit] = m[a][rr];
+          part_ml[2 * unit + 1] = l[a][rr];
+        }
       }
     }
-  }
+}
+
+size_t latent_mma_smem(int D, int mt) {
+  const int blocks = (D + 63) / 64, R = 16 * mt;
+  return (size_t)2 * blocks * kKeys * 128 + (size_t)blocks * R * 128 + (size_t)R * 128 + 2 * kWarps * R * sizeof(float);
 }
 
 }  // namespace
@@ -235,9 +276,18 @@ extern "C" int ib_latent_combine(const float* part_o, const float* part_ml, void
 // 1 when the tensor-core kernel takes these sizes (bfloat16 cache rows of D values of which the first `rank` are the latent).
 extern "C" int ib_latent_attention_mma_supports(int rank, int D) { return rank > 0 && rank % 16 == 0 && D % 16 == 0 && rank <= D && rank <= 512 && D <= 576; }
 
-extern "C" int ib_latent_attention_mma(const float* q, const IbKvView* kv, const int* positions, const int* seg_of_token, const int* units, int n_units, float scale,
-                                       void* out, float* part_o, float* part_ml, int T, int heads, int rank, int n_slices, int slice_keys, unsigned* status,
-                                       cudaStream_t stream) {
+// How many query rows a CTA of the tensor-core kernel holds for these sizes when a step has `rows_wanted` rows that can share key tiles
+// (the heads of a token, times the consecutive tokens of a prompt portion): 16, 32 or 64, bounded by registers (a latent above 256
+// values: 32) and by shared memory (two key tiles, the queries and the weights must fit).
+extern "C" int ib_latent_attention_mma_rows(int rank, int D, int rows_wanted) {
+  int mt = rank > 256 ? 2 : 4;
+  while (mt > 1 && (16 * (mt / 2) >= rows_wanted || latent_mma_smem(D, mt) > 200 * 1024)) mt /= 2;
+  return 16 * mt;
+}
+
+extern "C" int ib_latent_attention_mma(const float* q, const IbKvView* kv, const int* positions, const int* seg_of_token, const int* units, int n_units, int rows,
+                                       float scale, void* out, float* part_o, float* part_ml, int T, int heads, int rank, int n_slices, int slice_keys,
+                                       unsigned* status, cudaStream_t stream) {
   if (T == 0 || n_units == 0) return 0;
   IB_CHECK_ARG(kv && kv->base && kv->block_table && kv->kv_heads == 1 && kv->dtype == IB_BF16, "latent_attention_mma: a bfloat16 cache of one row per token is needed");
   const int D = kv->head_dim;
@@ -247,19 +297,27 @@ extern "C" int ib_latent_attention_mma(const float* q, const IbKvView* kv, const
   IB_CHECK_ARG(n_slices == 1 || (part_o && part_ml), "latent_attention_mma: slices need scratch");
   IB_CHECK_ARG(n_units <= 65535 && n_slices <= 65535, "latent_attention_mma: %d units or %d slices exceed the grid limit", n_units, n_slices);
   IB_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)kv->base % 16 == 0) && (kv->page_stride % 8 == 0), "latent_attention_mma: pointers must be 16-byte aligned");
-  const int blocks = (D + 63) / 64;
-  const size_t smem = (size_t)2 * blocks * kKeys * 128 + (size_t)blocks * kRows * 128 + kRows * 128 + 2 * kWarps * kRows * sizeof(float);
-  const int hpc = heads < kRows ? heads : kRows;
+  IB_CHECK_ARG((rows == 16 || rows == 32 || rows == 64) && !(rows == 64 && rank > 256), "latent_attention_mma: %d query rows a CTA (16, 32, or 64 up to a latent of 256)", rows);
+  const int mt = rows / 16;
+  const size_t smem = latent_mma_smem(D, mt);
+  IB_CHECK_ARG(smem <= 220 * 1024, "latent_attention_mma: %d rows of %d values need %zu bytes of shared memory", rows, D, smem);
+  const int hpc = heads < rows ? heads : rows;
   dim3 grid((heads + hpc - 1) / hpc, n_units, n_slices);
   auto go = [&](auto kernel) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ib::launch(kernel, grid, kWarps * 32, smem, stream, q, *kv, positions, seg_of_token, (const int2*)units, scale, (__nv_bfloat16*)out, part_o, part_ml, heads, rank, D,
                n_slices, slice_keys, status);
   };
-  if (rank <= 64) go(latent_attention_mma_kernel<1>);
-  else if (rank <= 128) go(latent_attention_mma_kernel<2>);
-  else if (rank <= 256) go(latent_attention_mma_kernel<4>);
-  else go(latent_attention_mma_kernel<8>);
+  auto pick = [&](auto nch) {
+    constexpr int NCH = decltype(nch)::value;
+    if (mt == 1) go(latent_attention_mma_kernel<NCH, 1>);
+    else if (mt == 2) go(latent_attention_mma_kernel<NCH, 2>);
+    else if constexpr (NCH <= 4) go(latent_attention_mma_kernel<NCH, 4>);
+  };
+  if (rank <= 64) pick(std::integral_constant<int, 1>());
+  else if (rank <= 128) pick(std::integral_constant<int, 2>());
+  else if (rank <= 256) pick(std::integral_constant<int, 4>());
+  else pick(std::integral_constant<int, 8>());
   IB_CHECK_LAUNCH("latent_attention_mma");
   if (n_slices > 1) return ib_latent_combine(part_o, part_ml, out, IB_BF16, T * heads, rank, n_slices, stream);
   return 0;

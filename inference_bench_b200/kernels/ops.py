@@ -350,7 +350,12 @@ def latent_attention(q_full: torch.Tensor, kv: KvLayerView, positions: torch.Ten
            dtype_code(out.dtype), _ptr(part_o), _ptr(part_ml), T, heads, rank, n_slices, slice_keys, status.data_ptr(), _stream())
 
 
-L.register("ib_latent_attention_mma", [L._p, C.POINTER(L.KvView), L._p, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_latent_attention_mma", [L._p, C.POINTER(L.KvView), L._p, L._p, L._p, L._i, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+
+
+def latent_attention_mma_rows(rank: int, row: int, rows_wanted: int) -> int:
+    """Query rows a CTA of the tensor-core kernel holds (16, 32 or 64) when `rows_wanted` rows of a step can share key tiles."""
+    return int(L.load().ib_latent_attention_mma_rows(int(rank), int(row), int(rows_wanted)))
 
 
 def latent_attention_mma_supports(rank: int, row: int) -> bool:
@@ -358,9 +363,10 @@ def latent_attention_mma_supports(rank: int, row: int) -> bool:
 
 
 def latent_attention_mma(q_full: torch.Tensor, kv: KvLayerView, positions: torch.Tensor, seg_of_token: torch.Tensor, units: Optional[torch.Tensor], scale: float,
-                         out: torch.Tensor, rank: int, n_slices: int, slice_keys: int, scratch, status: torch.Tensor) -> None:
-    """The same as `latent_attention` on the tensor cores (bfloat16 cache and output). units: None (a CTA per token) or int32 [n, 2] of
-    (first token, tokens): runs of consecutive tokens of one request that share a CTA's 16 query rows (fewer than 16 heads)."""
+                         out: torch.Tensor, rank: int, n_slices: int, slice_keys: int, scratch, status: torch.Tensor, rows: int = 16) -> None:
+    """The same as `latent_attention` on the tensor cores (bfloat16 cache and output). rows: query rows a CTA holds (16, 32 or 64).
+    units: None (a CTA per token) or int32 [n, 2] of (first token, tokens): runs of consecutive tokens of one request that share a
+    CTA's rows (at most rows // heads tokens each)."""
     T, heads, D = q_full.shape
     _check("q_full", q_full, torch.float32)
     _check("out", out, torch.bfloat16, (T, heads, rank))
@@ -378,7 +384,7 @@ def latent_attention_mma(q_full: torch.Tensor, kv: KvLayerView, positions: torch
         if part_o.numel() < T * heads * n_slices * rank or part_ml.numel() < T * heads * n_slices * 2:
             raise L.KernelError("latent_attention_mma: the scratch for the slices is too small")
         L.launches += 1
-    L.call("ib_latent_attention_mma", q_full.data_ptr(), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), _ptr(units), n_units, float(scale),
+    L.call("ib_latent_attention_mma", q_full.data_ptr(), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), _ptr(units), n_units, int(rows), float(scale),
            out.data_ptr(), _ptr(part_o), _ptr(part_ml), T, heads, rank, n_slices, slice_keys, status.data_ptr(), _stream())
 
 

@@ -81,12 +81,17 @@ class LatentAttention(base.Mixer):
             ctx.memo[key] = out
         return ctx.memo[key]
 
-    def _units(self, ctx):
-        """For the tensor-core kernel with fewer than 16 heads: runs of consecutive tokens of one request that fill a CTA's 16 query
-        rows, int32 [n, 2] of (first token, tokens) on the device; None when every token is a unit of its own."""
-        per = 16 // self.heads
-        if per <= 1 or ctx.fixed_shape or ctx.max_segment_len == 1:
-            return None
+    def _rows_and_units(self, ctx):
+        """For the tensor-core kernel: (query rows a CTA holds, runs of consecutive tokens of one request that fill them as int32 [n, 2]
+        of (first token, tokens) on the device, or None when every token is a unit of its own)."""
+        longest = 1 if ctx.fixed_shape else ctx.max_segment_len
+        rows = ops.latent_attention_mma_rows(self.kv_rank, self.kv_rank + self.rot_dim, self.heads * longest)
+        per = rows // self.heads
+        if per <= 1 or longest == 1:
+            return rows, None
+        return rows, self._units(ctx, per)
+
+    def _units(self, ctx, per):
         key = ("latent units", per)
         if key not in ctx.memo:
             runs = []
@@ -123,7 +128,8 @@ class LatentAttention(base.Mixer):
             scratch = ctx.memo[skey]
         u = rt.empty((T, H, r))
         if self._tensor_cores(rt):
-            ops.latent_attention_mma(q_full, cache, ctx.positions, ctx.seg_of_token, self._units(ctx), self.scale, u, r, n_slices, slice_keys, scratch, rt.status)
+            rows, units = self._rows_and_units(ctx)
+            ops.latent_attention_mma(q_full, cache, ctx.positions, ctx.seg_of_token, units, self.scale, u, r, n_slices, slice_keys, scratch, rt.status, rows)
         else:
             ops.latent_attention(q_full, cache, ctx.positions, ctx.seg_of_token, self.scale, u, r, n_slices, slice_keys, scratch, rt.status)
         v = rt.empty((T, H, self.vdim))

@@ -114,12 +114,15 @@ def test_latent_attention_kernel_far_keys_page_borders_and_the_causal_edge(rt32,
         if dtype == torch.bfloat16 and ops.latent_attention_mma_supports(rank, rank + rot) and slice_keys % 64 == 0:
             # the tensor-core kernel rounds the queries to bfloat16 too: compare with the plain sum over those
             want16 = _plain_latent_rows(cache, q.to(torch.bfloat16).float(), rows, rank, scale)
-            per = max(1, 16 // H)
-            for units in ([None] if per == 1 else [None, torch.tensor([(t, min(per, T - t)) for t in range(0, T, per)], dtype=torch.int32, device=DEV)]):
-                out = torch.full((T, H, rank), 9.0, dtype=dtype, device=DEV)
-                ops.latent_attention_mma(_f32(q), view, pos, seg, units, scale, out, rank, n_slices, slice_keys, scratch, rt32.status)
-                err = (out.cpu().double() - want16).abs().max().item()
-                assert err < 3e-2, f"tensor cores, {n_slices} slices, {'a CTA per token' if units is None else 'tokens sharing a CTA'}: {err}"
+            for cta_rows in (16, 32, 64):   # query rows a CTA holds: the heads of one token, or of several consecutive tokens
+                if cta_rows > ops.latent_attention_mma_rows(rank, rank + rot, 64):
+                    continue
+                per = max(1, cta_rows // H)
+                for units in ([None] if per == 1 else [None, torch.tensor([(t, min(per, T - t)) for t in range(0, T, per)], dtype=torch.int32, device=DEV)]):
+                    out = torch.full((T, H, rank), 9.0, dtype=dtype, device=DEV)
+                    ops.latent_attention_mma(_f32(q), view, pos, seg, units, scale, out, rank, n_slices, slice_keys, scratch, rt32.status, cta_rows)
+                    err = (out.cpu().double() - want16).abs().max().item()
+                    assert err < 3e-2, f"tensor cores, {cta_rows} rows a CTA, {n_slices} slices, {'a CTA per token' if units is None else 'tokens sharing a CTA'}: {err}"
     rt32.check_status()
 
 
