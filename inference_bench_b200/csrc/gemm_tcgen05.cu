@@ -47,7 +47,12 @@ struct Tile {
 template <int BN, int MT, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, void* __restrict__ out_, int T,
-                        int N, int K, int ktiles_per_split, int second_off, unsigned long long wait_ns, int starve, unsigned* __restrict__ status) {
+                        int N, int K, int ktiles_per_split, int second_off, unsigned long long wait_ns, int starve, unsigned* __restrict__ status,
+                        const int* __restrict__ grp_offsets, const int* __restrict__ grp_tiles, int n_groups, int grp_w_rows) {
+  // grp_offsets != nullptr: the rows of x are regrouped (rows grp_offsets[e] .. grp_offsets[e + 1] belong to group e, whose matrix is rows
+  // e * grp_w_rows .. of w) and blockIdx.x counts token tiles over all groups: grp_tiles[e] is the first tile of group e, grp_tiles[n_groups]
+  // their number (the grid is an upper bound; the CTAs beyond it leave at once). A tile never crosses a group's end: rows past it are
+  // multiplied and not stored.
   // wait_ns: the limit of every wait below. starve != 0 (the wait-limit test only): the copying warp sends nothing, so that
   // the waits run out the way they would if a copy never landed, and the kernel has to unwind through its ordinary path.
   using TL = Tile<BN, MT>;
@@ -65,7 +70,22 @@ __global__ void __launch_bounds__(kThreads, 1)
   // (token tiles vary fastest in the grid: the CTAs that share a block of W run together, so W comes
   // from memory once and the much smaller x stays in L2)
   const int n0 = blockIdx.y * (EPI == EPI_SWIGLU_HALF ? BM / 2 : EPI == EPI_SWIGLU ? BM : BM * MT);
-  const int t0 = blockIdx.x * BN, split = blockIdx.z;
+  const int split = blockIdx.z;
+  int t0 = blockIdx.x * BN, t_end = T, w_row0 = 0;
+  if (grp_offsets) {
+    ib::pdl_wait();   // the table is the work of the kernels before
+    const int b = blockIdx.x;
+    if (b >= grp_tiles[n_groups]) return;
+    int lo = 0, hi = n_groups;   // the last group whose first tile is at or before b
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (grp_tiles[mid] <= b) lo = mid;
+      else hi = mid;
+    }
+    t0 = grp_offsets[lo] + (b - grp_tiles[lo]) * BN;
+    t_end = grp_offsets[lo + 1];
+    w_row0 = lo * grp_w_rows;
+  }
   const int total_kt = (K + BK - 1) / BK;
   const int kt_begin = split * ktiles_per_split;
   const int kt_end = min(total_kt, kt_begin + ktiles_per_split);
@@ -97,11 +117,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       // for the kernel that produces x, then send the x tiles after.
       auto load_w = [&](uint8_t* a, int kt, uint64_t* bar) {   // this CTA's rows of W for k-tile kt
         if constexpr (EPI == EPI_SWIGLU_HALF) {   // tmap_w's box has 64 rows here: gate rows, then the up rows second_off further on
-          sm100::tma_load_2d(a, &tmap_w, kt * BK, n0, bar);
-          sm100::tma_load_2d(a + TL::kABytes / 2, &tmap_w, kt * BK, n0 + second_off, bar);
+          sm100::tma_load_2d(a, &tmap_w, kt * BK, w_row0 + n0, bar);
+          sm100::tma_load_2d(a + TL::kABytes / 2, &tmap_w, kt * BK, w_row0 + n0 + second_off, bar);
         } else {
 #pragma unroll
-          for (int m = 0; m < MT; m++) sm100::tma_load_2d(a + m * TL::kABytes, &tmap_w, kt * BK, n0 + m * second_off, bar);
+          for (int m = 0; m < MT; m++) sm100::tma_load_2d(a + m * TL::kABytes, &tmap_w, kt * BK, w_row0 + n0 + m * second_off, bar);
         }
       };
       const int first = min(nkt, STAGES);
@@ -186,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int c = 0; c < CH; c++) {
               const int t = t0 + c0 + c;
-              if (t < T) dst[(size_t)t * N + n] = __uint_as_float(r[c]);
+              if (t < t_end) dst[(size_t)t * N + n] = __uint_as_float(r[c]);
             }
           }
         }
@@ -211,7 +231,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int c = 0; c < CH; c++) {
             const int t = t0 + c0 + c;
             const float gv = __uint_as_float(g[c]), uv = __uint_as_float(u[c]);
-            if (t < T) dst[(size_t)t * N + n] = __float2bfloat16_rn(__fdividef(gv, 1.f + __expf(-gv)) * uv);
+            if (t < t_end) dst[(size_t)t * N + n] = __float2bfloat16_rn(__fdividef(gv, 1.f + __expf(-gv)) * uv);
           }
         }
       }
@@ -245,7 +265,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int c = 0; c < CH; c++) {
               const int t = t0 + c0 + c;
               const float gv = __uint_as_float(r[c]), uv = up_s[(c0 + c) * 64 + q * 32 + lane];
-              if (t < T) dst[(size_t)t * N + n] = __float2bfloat16_rn(__fdividef(gv, 1.f + __expf(-gv)) * uv);
+              if (t < t_end) dst[(size_t)t * N + n] = __float2bfloat16_rn(__fdividef(gv, 1.f + __expf(-gv)) * uv);
             }
           }
         }
@@ -277,9 +297,15 @@ int make_tmap(CUtensorMap* m, const void* ptr, int rows, int K, int box_rows) {
   return 0;
 }
 
+struct Groups {   // regrouped rows (see the kernel): nullptr offsets = one matrix for all rows
+  const int* offsets = nullptr;
+  const int* tiles = nullptr;
+  int n = 0, w_rows = 0;
+};
+
 template <int BN, int MT, int EPI>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int splits, int kt_per_split, int second_off,
-           unsigned* status, cudaStream_t stream, int starve = 0) {
+           unsigned* status, cudaStream_t stream, int starve = 0, Groups grp = Groups()) {
   using TL = Tile<BN, MT>;
   static bool configured = false;
   if (!configured) {
@@ -288,9 +314,10 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
     configured = true;
   }
   const int cols_per_cta = EPI == EPI_SWIGLU_HALF ? BM / 2 : EPI == EPI_SWIGLU ? BM : BM * MT;
-  dim3 grid((T + BN - 1) / BN, (N + cols_per_cta - 1) / cols_per_cta, splits);
+  dim3 grid(grp.offsets ? T / BN + grp.n : (T + BN - 1) / BN, (N + cols_per_cta - 1) / cols_per_cta, splits);
   IB_CHECK_ARG(grid.y <= 65535, "gemm_tcgen05: N=%d gives more than 65535 row blocks", N);
-  ib::launch(gemm_tcgen05_kernel<BN, MT, EPI>, grid, kThreads, TL::kSmemBytes, stream, tw, tx, out, T, N, K, kt_per_split, second_off, ib_wait_limit_ns(), starve, status);
+  ib::launch(gemm_tcgen05_kernel<BN, MT, EPI>, grid, kThreads, TL::kSmemBytes, stream, tw, tx, out, T, N, K, kt_per_split, second_off, ib_wait_limit_ns(), starve, status,
+             grp.offsets, grp.tiles, grp.n, grp.w_rows);
   IB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
 }
@@ -374,5 +401,53 @@ extern "C" int ib_gemm_swiglu_tcgen05(const void* x, const void* w, void* act, i
     case 128: return launch<128, 2, EPI_SWIGLU>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
     case 256: return launch<256, 2, EPI_SWIGLU>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
     default: return ib_set_error("gemm_swiglu_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", bn);
+  }
+}
+
+// The same products on regrouped rows (routed experts): x [R, K] holds the rows of expert e at offsets[e] .. offsets[e + 1], w [E, N, K]
+// one matrix per expert, tiles[e] the first token tile (of bn rows) of expert e and tiles[E] their number. out [R, N] float32.
+extern "C" int ib_gemm_grouped_tcgen05(const void* x, const void* w, float* out, int R, int N, int K, int bn, const int* offsets, const int* tiles, int E,
+                                       unsigned* status, cudaStream_t stream) {
+  if (R == 0 || N == 0) return 0;
+  if (check_common("gemm_grouped_tcgen05", x, w, R, N, K, bn)) return 1;
+  IB_CHECK_ARG(E > 0 && offsets && tiles, "gemm_grouped_tcgen05: the groups' tables are missing");
+  const int total_kt = (K + BK - 1) / BK;
+  CUtensorMap tw, tx;
+  if (make_tmap(&tw, w, E * N, K, BM)) return 1;
+  if (make_tmap(&tx, x, R, K, bn)) return 1;
+  Groups g;
+  g.offsets = offsets, g.tiles = tiles, g.n = E, g.w_rows = N;
+  switch (bn) {
+    case 16: return launch<16, 1, EPI_STORE>(tw, tx, out, R, N, K, 1, total_kt, 0, status, stream, 0, g);
+    case 32: return launch<32, 1, EPI_STORE>(tw, tx, out, R, N, K, 1, total_kt, 0, status, stream, 0, g);
+    case 64: return launch<64, 1, EPI_STORE>(tw, tx, out, R, N, K, 1, total_kt, 0, status, stream, 0, g);
+    case 128: return launch<128, 1, EPI_STORE>(tw, tx, out, R, N, K, 1, total_kt, 0, status, stream, 0, g);
+    default: return ib_set_error("gemm_grouped_tcgen05: token tile %d is not one of 16, 32, 64, 128", bn);
+  }
+}
+
+// w [E, 2 I, K]: every expert's gate rows then its up rows; act [R, I] bfloat16 = silu(x gate^T) * (x up^T) per expert.
+// bn 16 or 32: 64 gate rows and their up rows in one accumulator (I a multiple of 64); bn 64 or 128: two accumulators.
+extern "C" int ib_gemm_grouped_swiglu_tcgen05(const void* x, const void* w, void* act, int R, int I, int K, int bn, const int* offsets, const int* tiles, int E,
+                                              unsigned* status, cudaStream_t stream) {
+  if (R == 0 || I == 0) return 0;
+  if (check_common("gemm_grouped_swiglu_tcgen05", x, w, R, I, K, bn)) return 1;
+  IB_CHECK_ARG(E > 0 && offsets && tiles, "gemm_grouped_swiglu_tcgen05: the groups' tables are missing");
+  const int total_kt = (K + BK - 1) / BK;
+  CUtensorMap tw, tx;
+  Groups g;
+  g.offsets = offsets, g.tiles = tiles, g.n = E, g.w_rows = 2 * I;
+  if (make_tmap(&tx, x, R, K, bn)) return 1;
+  if (bn == 16 || bn == 32) {
+    IB_CHECK_ARG(I % 64 == 0, "gemm_grouped_swiglu_tcgen05: with %d tokens per CTA the inner size must be a multiple of 64, not %d", bn, I);
+    if (make_tmap(&tw, w, E * 2 * I, K, BM / 2)) return 1;
+    if (bn == 16) return launch<16, 1, EPI_SWIGLU_HALF>(tw, tx, act, R, I, K, 1, total_kt, I, status, stream, 0, g);
+    return launch<32, 1, EPI_SWIGLU_HALF>(tw, tx, act, R, I, K, 1, total_kt, I, status, stream, 0, g);
+  }
+  if (make_tmap(&tw, w, E * 2 * I, K, BM)) return 1;
+  switch (bn) {
+    case 64: return launch<64, 2, EPI_SWIGLU>(tw, tx, act, R, I, K, 1, total_kt, I, status, stream, 0, g);
+    case 128: return launch<128, 2, EPI_SWIGLU>(tw, tx, act, R, I, K, 1, total_kt, I, status, stream, 0, g);
+    default: return ib_set_error("gemm_grouped_swiglu_tcgen05: token tile %d is not one of 16, 32, 64, 128", bn);
   }
 }

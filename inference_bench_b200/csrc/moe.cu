@@ -102,8 +102,8 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int P, size_t
 
 constexpr int SM_ = 64;   // rows of a tile of the grouped product
 
-__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, int R, int top, int E, int* __restrict__ offsets, int* __restrict__ tile_start,
-                                                        int* __restrict__ row_of_pair, int* __restrict__ token_of_row) {
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, int R, int top, int E, int tile_rows, int* __restrict__ offsets,
+                                                        int* __restrict__ tile_start, int* __restrict__ row_of_pair, int* __restrict__ token_of_row) {
   extern __shared__ int si[];   // counts[E], fill[E], start[E + 1]
   int* counts = si;
   int* fill = si + E;
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
       offsets[e] = a;
       tile_start[e] = tl;
       a += counts[e];
-      tl += (counts[e] + SM_ - 1) / SM_;
+      tl += (counts[e] + tile_rows - 1) / tile_rows;
     }
     start[E] = a;
     offsets[E] = a;
@@ -260,6 +260,15 @@ __global__ void __launch_bounds__(256) gemm_grouped_kernel(const X* __restrict__
   }
 }
 
+// out[r] = x[src_row[r]]: the step's rows in the experts' order (16 bytes a thread; K a multiple of 8).
+__global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ src_row, uint4* __restrict__ out, int chunks) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int r = blockIdx.x;
+  const uint4* src = x + (size_t)src_row[r] * chunks;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < chunks; c += gridDim.y * blockDim.x) out[(size_t)r * chunks + c] = src[c];
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair, const float* __restrict__ wt, int top,
                                    const float* __restrict__ base, int P, size_t stride_p, float* __restrict__ out, int H) {
   ib::pdl_launch_dependents();
@@ -290,12 +299,15 @@ extern "C" int ib_moe_route(const float* logits, int P, long long stride_p, int 
 
 extern "C" int ib_moe_tile_rows() { return SM_; }
 
-extern "C" int ib_moe_sort(const int* idx, int R, int top, int E, int* offsets, int* tile_start, int* row_of_pair, int* token_of_row, cudaStream_t stream) {
+// tile_rows: the rows of a tile of the product that will run on the regrouped rows (ib_moe_tile_rows() for this file's and the m16n8k16
+// kernel; the token tile of the tcgen05 kernel).
+extern "C" int ib_moe_sort(const int* idx, int R, int top, int E, int tile_rows, int* offsets, int* tile_start, int* row_of_pair, int* token_of_row,
+                           cudaStream_t stream) {
   if (R == 0) return 0;
-  IB_CHECK_ARG(R > 0 && top > 0 && E > 0, "moe_sort: bad sizes pairs=%d top=%d experts=%d", R, top, E);
+  IB_CHECK_ARG(R > 0 && top > 0 && E > 0 && tile_rows > 0, "moe_sort: bad sizes pairs=%d top=%d experts=%d tile=%d", R, top, E, tile_rows);
   const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
   IB_CHECK_ARG(smem <= 48 * 1024, "moe_sort: %d experts need %zu bytes of shared memory, more than 48 KiB", E, smem);
-  ib::launch(moe_sort_kernel, 1, 1024, smem, stream, idx, R, top, E, offsets, tile_start, row_of_pair, token_of_row);
+  ib::launch(moe_sort_kernel, 1, 1024, smem, stream, idx, R, top, E, tile_rows, offsets, tile_start, row_of_pair, token_of_row);
   IB_CHECK_LAUNCH("moe_sort");
   return 0;
 }
@@ -324,5 +336,15 @@ extern "C" int ib_moe_combine(const float* y, const int* row_of_pair, const floa
   dim3 grid(min((H + 255) / 256, 64), T);
   ib::launch(moe_combine_kernel, grid, 256, 0, stream, y, row_of_pair, wt, top, base, P, (size_t)stride_p, out, H);
   IB_CHECK_LAUNCH("moe_combine");
+  return 0;
+}
+
+extern "C" int ib_gather_rows(const void* x, const int* src_row, void* out, int R, int K, int elem_bytes, cudaStream_t stream) {
+  if (R == 0) return 0;
+  IB_CHECK_ARG(R > 0 && K > 0 && (K * elem_bytes) % 16 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0), "gather_rows: rows of %d bytes must be multiples of 16, aligned",
+               K * elem_bytes);
+  const int chunks = K * elem_bytes / 16;
+  ib::launch(gather_rows_kernel, dim3(R, min((chunks + 127) / 128, 8)), 128, 0, stream, (const uint4*)x, src_row, (uint4*)out, chunks);
+  IB_CHECK_LAUNCH("gather_rows");
   return 0;
 }

@@ -26,6 +26,9 @@ L.register("ib_gemm_swiglu_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L
 L.register("ib_gemm_tcgen05_2cta_add", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_qkv_tcgen05_2cta", [L._p, L._p, L._i, L._i, L._p, L._p, L._f, L._p, L._p, L._p, L._p, L._p, C.POINTER(L.KvView), L._i, L._i, L._p, L._p])
 
+L.register("ib_gemm_grouped_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._p, L._p, L._i, L._p, L._p])
+L.register("ib_gemm_grouped_swiglu_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._p, L._p, L._i, L._p, L._p])
+
 # Runtime options that steer the choice (config/runtime_options.py): `pair_min_tokens` (129: the fused gate/up product runs on the
 # persistent CTA-pair kernel, csrc/gemm_tcgen05_2cta.cu, from here on whatever its size), `pair_always_tokens` (2,048: every
 # product from here on; between the two, `plan` decides by its cost model) and `fuse_qkv_epilogue`.
@@ -245,3 +248,39 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, sta
     if bn is None:
         bn = 64 if T <= 64 else (128 if T <= 128 else 256)
     L.call("ib_gemm_swiglu_tcgen05", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), T, I, K, bn, 1 if half else 0, status.data_ptr(), ops._stream())
+
+
+# ---------------------------------------------------------------- products on regrouped rows (routed experts)
+def grouped_token_tile(rows: int, groups: int) -> int:
+    """Tokens per CTA for a product on `rows` regrouped rows of `groups` experts: the smallest tile that holds an expert's average share
+    (a function of the sizes only)."""
+    avg = -(-rows // groups)
+    return 16 if avg <= 16 else 32 if avg <= 32 else 64 if avg <= 64 else 128
+
+
+def grouped_supported(k: int, inter: int, bn: int) -> bool:
+    """Whether the tcgen05 kernel takes the experts' two products: inner sizes that are multiples of 8, and for tiles of 16 or 32 tokens
+    (64 gate rows and their up rows in one accumulator) an expert size that is a multiple of 64."""
+    return k % 8 == 0 and inter % 8 == 0 and (bn >= 64 or inter % 64 == 0)
+
+
+def gemm_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int, offsets: torch.Tensor, tiles: torch.Tensor, status: torch.Tensor) -> None:
+    """out [R, N] float32 = per expert w[e] x[r] for the regrouped rows x [R, K] (expert e's rows: offsets[e] .. offsets[e + 1]); w [E, N, K];
+    tiles: first token tile of `bn` rows of every expert, then their number (`ops.moe_sort` with tile_rows=bn)."""
+    R, K = x.shape
+    E, N, _ = w.shape
+    ops._check("x", x, torch.bfloat16)
+    ops._check("w", w, torch.bfloat16, (E, N, K))
+    ops._check("out", out, torch.float32, (R, N))
+    L.call("ib_gemm_grouped_tcgen05", x.data_ptr(), w.data_ptr(), out.data_ptr(), R, N, K, bn, offsets.data_ptr(), tiles.data_ptr(), E, status.data_ptr(), ops._stream())
+
+
+def gemm_grouped_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, bn: int, offsets: torch.Tensor, tiles: torch.Tensor, status: torch.Tensor) -> None:
+    """act [R, I] bfloat16 = silu(gate_e x) * (up_e x) per expert, w_gate_up [E, 2 I, K] = every expert's gate rows then its up rows."""
+    R, K = x.shape
+    E, I2, _ = w_gate_up.shape
+    ops._check("x", x, torch.bfloat16)
+    ops._check("w_gate_up", w_gate_up, torch.bfloat16, (E, I2, K))
+    ops._check("act", act, torch.bfloat16, (R, I2 // 2))
+    L.call("ib_gemm_grouped_swiglu_tcgen05", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), R, I2 // 2, K, bn, offsets.data_ptr(), tiles.data_ptr(), E,
+           status.data_ptr(), ops._stream())

@@ -390,7 +390,24 @@ def latent_attention_mma(q_full: torch.Tensor, kv: KvLayerView, positions: torch
 
 # ---------------------------------------------------------------- routed experts (csrc/moe.cu)
 L.register("ib_moe_route", [L._p, L._i, L._ll, L._i, L._i, L._i, L._i, L._i, L._f, L._i, L._p, L._p, L._p])
-L.register("ib_moe_sort", [L._p, L._i, L._i, L._i, L._p, L._p, L._p, L._p, L._p])
+L.register("ib_moe_sort", [L._p, L._i, L._i, L._i, L._i, L._p, L._p, L._p, L._p, L._p])
+L.register("ib_gather_rows", [L._p, L._p, L._p, L._i, L._i, L._i, L._p])
+
+
+def moe_tile_rows() -> int:
+    """Rows of a tile of the FMA and m16n8k16 kernels for regrouped rows."""
+    return int(L.load().ib_moe_tile_rows())
+
+
+def gather_rows(x: torch.Tensor, src_row: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = x[src_row[r]] (rows of a multiple of 16 bytes)."""
+    R, K = out.shape
+    _check("x", x, out.dtype)
+    _check("out", out)
+    _check("src_row", src_row, torch.int32, (R,))
+    if x.shape[1] != K:
+        raise L.KernelError(f"gather_rows: x has {x.shape[1]} columns, out {K}")
+    L.call("ib_gather_rows", x.data_ptr(), src_row.data_ptr(), out.data_ptr(), R, K, x.element_size(), _stream())
 L.register("ib_gemm_grouped", [L._p, L._i, L._p, L._p, L._i, L._p, L._i, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p])
 L.register("ib_moe_combine", [L._p, L._p, L._p, L._i, L._p, L._i, L._ll, L._p, L._i, L._i, L._p])
 
@@ -404,14 +421,18 @@ def moe_route(logits: torch.Tensor, n_groups: int, keep: int, top: int, route_sc
     L.call("ib_moe_route", logits.data_ptr(), P, T * E, T, E, n_groups, keep, top, float(route_scale), 1 if renorm else 0, idx.data_ptr(), wt.data_ptr(), _stream())
 
 
-def moe_sort(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, tile_start: torch.Tensor, row_of_pair: torch.Tensor, token_of_row: torch.Tensor) -> None:
+def moe_sort(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, tile_start: torch.Tensor, row_of_pair: torch.Tensor, token_of_row: torch.Tensor,
+             tile_rows: Optional[int] = None) -> None:
+    """Regroup the step's (token, choice) pairs by expert: offsets[e] .. offsets[e + 1] are expert e's rows, row_of_pair / token_of_row map
+    between pairs and rows, tile_start[e] is expert e's first tile of `tile_rows` rows (default: the FMA and m16n8k16 kernels' 64)."""
     T, top = idx.shape
+    tile_rows = tile_rows or moe_tile_rows()
     _check("idx", idx, torch.int32)
     _check("offsets", offsets, torch.int32, (n_experts + 1,))
     _check("tile_start", tile_start, torch.int32, (n_experts + 1,))
     _check("row_of_pair", row_of_pair, torch.int32, (T * top,))
     _check("token_of_row", token_of_row, torch.int32, (T * top,))
-    L.call("ib_moe_sort", idx.data_ptr(), T * top, top, n_experts, offsets.data_ptr(), tile_start.data_ptr(), row_of_pair.data_ptr(), token_of_row.data_ptr(), _stream())
+    L.call("ib_moe_sort", idx.data_ptr(), T * top, top, n_experts, int(tile_rows), offsets.data_ptr(), tile_start.data_ptr(), row_of_pair.data_ptr(), token_of_row.data_ptr(), _stream())
 
 
 def gemm_grouped(x: torch.Tensor, src_row: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, tile_start: torch.Tensor,

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import torch
 
+from ..kernels import gemm_tcgen05 as G
 from ..kernels import ops
 from . import base
 from .base import WeightSpec
@@ -60,12 +61,24 @@ class RoutedExperts(base.FeedForward):
         ops.moe_route(logits, self.groups, self.groups_keep, top, self.route_scale, self.renorm, idx, wt)
         offsets, tile_start = rt.empty((E + 1,), torch.int32), rt.empty((E + 1,), torch.int32)
         row_of_pair, token_of_row = rt.empty((R,), torch.int32), rt.empty((R,), torch.int32)
-        ops.moe_sort(idx, E, offsets, tile_start, row_of_pair, token_of_row)
+        how = rt.options.expert_gemm
+        bn = G.grouped_token_tile(R, E)
         act = rt.empty((R, self.expert_ff))
-        tc = rt.options.expert_gemm != "simt"
-        ops.gemm_grouped(h, token_of_row, self.w_gu, act, offsets, tile_start, gated=True, tensor_cores=tc and ops.rows_mma_fits(h, self.w_gu))
         y = rt.empty((R, self.hidden), torch.float32)
-        ops.gemm_grouped(act, None, self.w_d, y, offsets, tile_start, gated=False, tensor_cores=tc and ops.rows_mma_fits(act, self.w_d))
+        if how in ("auto", "tcgen05") and rt.act_dtype == torch.bfloat16 and rt.gemm != "simt" and G.grouped_supported(self.hidden, self.expert_ff, bn):
+            # the tcgen05 kernel of the single-matrix products, its tiles taking their expert from the tile table
+            ops.moe_sort(idx, E, offsets, tile_start, row_of_pair, token_of_row, tile_rows=bn)
+            xs = rt.empty((R, self.hidden))
+            ops.gather_rows(h, token_of_row, xs)
+            G.gemm_grouped_swiglu(xs, self.w_gu, act, bn, offsets, tile_start, rt.status)
+            G.gemm_grouped(act, self.w_d, y, bn, offsets, tile_start, rt.status)
+        else:
+            if how == "tcgen05":
+                raise ValueError(f"expert_gemm = \"tcgen05\" needs bfloat16 and inner sizes that are multiples of 8 (of 64 for few tokens), got {self.hidden} and {self.expert_ff}")
+            tc = how != "simt"
+            ops.moe_sort(idx, E, offsets, tile_start, row_of_pair, token_of_row)
+            ops.gemm_grouped(h, token_of_row, self.w_gu, act, offsets, tile_start, gated=True, tensor_cores=tc and ops.rows_mma_fits(h, self.w_gu))
+            ops.gemm_grouped(act, None, self.w_d, y, offsets, tile_start, gated=False, tensor_cores=tc and ops.rows_mma_fits(act, self.w_d))
         shared = rt.linear(rt.gate_up_act(h, self.shared_gu), self.shared_d) if self.shared_ff else None
         out = rt.empty((1, T, self.hidden), torch.float32)
         ops.moe_combine(y, row_of_pair, wt, shared, out[0])

@@ -117,7 +117,7 @@ class LatentAttention(base.Mixer):
         q_full = rt.empty((T, H, r + rot), torch.float32)
         ops.latent_prepare(qd, self.c_norm, self.norm_eps, cos, sin, ctx.positions, ctx.seg_of_token, q_nope, q_full, cache, H, self.dim, rot, r,
                            self.own_kv, rt.status)
-        tc = rt.options.expert_gemm != "simt"
+        tc = rt.options.expert_gemm != "simt"   # (the per-head maps have the m16n8k16 kernel and the FMA kernel)
         ops.gemm_heads(q_nope, self.wuk_t, q_full, r, tensor_cores=tc and ops.rows_mma_fits(q_nope, self.wuk_t))
         n_slices, slice_keys = self._slices(ctx, cache.c_view())
         scratch = None

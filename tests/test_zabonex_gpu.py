@@ -210,7 +210,7 @@ def test_router_choice(rt32, E, groups, keep, top, scale):
 
 
 @pytest.mark.parametrize("T", [1, 2, 9, 150])
-@pytest.mark.parametrize("E,top,W,F", [(5, 1, 80, 40), (16, 4, 132, 36), (3, 3, 64, 70), (7, 2, 200, 136)])
+@pytest.mark.parametrize("E,top,W,F", [(5, 1, 80, 40), (16, 4, 132, 36), (3, 3, 64, 70), (7, 2, 200, 136), (6, 2, 136, 192)])
 def test_experts_on_regrouped_rows(rt32, T, E, top, W, F):
     """Regrouping by expert, the experts' two products and the weighted sum, against the plain loop over tokens; the rows an expert
     gets span several tiles for the largest T and some experts get none for the smallest."""
@@ -253,6 +253,21 @@ def test_experts_on_regrouped_rows(rt32, T, E, top, W, F):
         ops.gemm_grouped(act16, None, db, y, offsets, tile_start, gated=False, tensor_cores=True)
         ops.moe_combine(y, row_of_pair, _f32(wt), _f32(base), out)
         assert torch.allclose(out.cpu().double(), want16, atol=2e-3)
+        # and on tcgen05: the rows gathered into the experts' order first, token tiles of every size the kernel has
+        from inference_bench_b200.kernels import gemm_tcgen05 as G
+        for bn in (16, 32, 64, 128):
+            if not G.grouped_supported(W, F, bn):
+                continue
+            ops.moe_sort(idx_d, E, offsets, tile_start, row_of_pair, token_of_row, tile_rows=bn)
+            xs = torch.empty((R, W), device=DEV, dtype=torch.bfloat16)
+            ops.gather_rows(hb, token_of_row, xs)
+            assert torch.equal(xs, hb[token_of_row.long()])
+            act16.fill_(7.0), y.fill_(7.0)
+            G.gemm_grouped_swiglu(xs, gub, act16, bn, offsets, tile_start, rt32.status)
+            G.gemm_grouped(act16, db, y, bn, offsets, tile_start, rt32.status)
+            ops.moe_combine(y, row_of_pair, _f32(wt), _f32(base), out)
+            assert torch.allclose(out.cpu().double(), want16, atol=3e-3), f"token tile {bn}"
+        rt32.check_status()
 
 
 # ------------------------------------------------------------------------------------------ whole models
