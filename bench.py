@@ -419,7 +419,7 @@ DESIGN_SIZES = {
     "lite": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, dense_ff=10944, experts=64, top=6, expert_ff=1408, shared_ff=2816, groups=(8, 4), vocab=32768),
 }
 DESIGN_KINDS = {   # kinds of kernel by the library entry points that launch them
-    "zabonex": {"attention": ["ib_latent_attention", "ib_latent_attention_mma"], "experts": ["ib_gemm_grouped", "ib_gemm_grouped_mma"],
+    "zabonex": {"attention": ["ib_latent_attention", "ib_latent_attention_mma"], "experts": ["ib_gemm_grouped", "ib_gemm_grouped_mma", "ib_gemm_grouped_tcgen05", "ib_gemm_grouped_swiglu_tcgen05", "ib_gather_rows"],
                 "heads": ["ib_gemm_heads", "ib_gemm_heads_mma"], "route": ["ib_moe_route", "ib_moe_sort", "ib_moe_combine"],
                 "norm": ["ib_norm_residual", "ib_latent_prepare", "ib_cast_rows"], "gemm": LEAVE_OUT["gemm"]},
     "qwen3": {"attention": LEAVE_OUT["attention"], "norm": LEAVE_OUT["norm"] + LEAVE_OUT["qk"], "gemm": LEAVE_OUT["gemm"] + LEAVE_OUT["qkv"]},

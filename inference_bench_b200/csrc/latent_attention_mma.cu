@@ -43,9 +43,11 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
   const int hpc = H < R ? H : R;                             // heads a CTA covers
   const int h0 = blockIdx.x * hpc;
-  int tok0 = blockIdx.y, ntok = 1;
+  // the last units first: in a prompt portion they see the most keys, and the short ones then fill the end of the launch
+  const int ui = gridDim.y - 1 - blockIdx.y;
+  int tok0 = ui, ntok = 1;
   if (units) {
-    const int2 u = units[blockIdx.y];
+    const int2 u = units[ui];
     tok0 = u.x, ntok = u.y;
   }
   const int slice = blockIdx.z;

@@ -6,7 +6,7 @@
 //    eligible experts with the largest s are chosen (ties: the lower index), each weighted s * route_scale, or
 //    s / (sum of the chosen s) * route_scale with `renorm`.
 //  * moe_sort: counts the (token, choice) pairs of every expert, lays the experts' rows out one after the other
-//    (offsets[e] .. offsets[e + 1]) and gives every pair its row; tile_start[e] is the first 64-row tile of expert e.
+//    (offsets[e] .. offsets[e + 1]) and gives every pair a row of its expert's range; tile_start[e] is the first tile of expert e.
 //  * gemm_grouped: out[r] = W[e(r)] x[src(r)] for every regrouped row r: a 64 x 64 tile belongs to one expert; float32
 //    FMA chains per output (a row's result does not depend on its place among the rows). With `gated`, W holds gate
 //    rows then up rows and the output is silu(gate) * up.
@@ -131,37 +131,14 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
     tile_start[E] = tl;
   }
   __syncthreads();
-  // A pair's row inside its expert's range is its rank among the expert's pairs in pair order, so the layout does not
-  // depend on the order threads run in: thread r counts the earlier pairs of the same expert in its own 1024-block by
-  // a shared scan per round.
-  for (int r0 = 0; r0 < R; r0 += blockDim.x) {
-    const int r = r0 + threadIdx.x;
-    int e = -1, before = 0;
-    if (r < R) {
-      e = idx[r];
-      if (e < 0 || e >= E) e = -1;
-    }
-    // rank inside this round: count lower threads with the same expert (warp ballot, then per-warp prefix through fill)
-    const unsigned peers = __match_any_sync(0xffffffffu, e);
-    const int lane = threadIdx.x & 31;
-    before = __popc(peers & ((1u << lane) - 1u));
-    const int in_warp = __popc(peers);
-    const bool leader = before == 0;
-    // warps take their turn in order, so that earlier warps' pairs come first
-    for (int w = 0; w < (int)(blockDim.x >> 5); w++) {
-      if ((int)(threadIdx.x >> 5) == w && e >= 0) {
-        int base = 0;
-        if (leader) {
-          base = fill[e];
-          fill[e] = base + in_warp;
-        }
-        base = __shfl_sync(peers, base, __ffs(peers) - 1);
-        const int row = start[e] + base + before;
-        row_of_pair[r] = row;
-        token_of_row[row] = r / top;
-      }
-      __syncthreads();
-    }
+  // A pair takes the next free row of its expert's range. Which pair gets which row depends on the order threads run in; no result
+  // does: every regrouped row is multiplied on its own, and the weighted sum goes back through row_of_pair in the order of the choices.
+  for (int r = threadIdx.x; r < R; r += blockDim.x) {
+    const int e = idx[r];
+    if (e < 0 || e >= E) continue;
+    const int row = start[e] + atomicAdd(&fill[e], 1);
+    row_of_pair[r] = row;
+    token_of_row[row] = r / top;
   }
 }
 

@@ -73,8 +73,8 @@ class LatentAttention(base.Mixer):
             out = (1, 1 << 30)
             if single:
                 max_keys = view.table_stride * view.page_size if ctx.fixed_shape else int(np.max(ctx.h_positions)) + 1
-                ctas = ctx.n_tokens * -(-self.heads // 8)
-                n = max(1, min(2 * ctx.rt.sm_count // ctas, -(-max_keys // 64)))
+                ctas = ctx.n_tokens * -(-self.heads // (16 if self._tensor_cores(ctx.rt) else 8))
+                n = max(1, min(ctx.rt.sm_count // ctas, -(-max_keys // 128)))   # two key tiles a slice at least: the second arrives while the first is used
                 if n > 1:
                     per = -(-(-(-max_keys // n)) // 64) * 64
                     out = (-(-max_keys // per), per)
