@@ -2,14 +2,14 @@
 // (a head's query [Wuk^T q_n | q_r] against the cached rows [c | kr], softmax in float32, weighted sum of the latents c),
 // for row sizes that are multiples of 16.
 //
-// A CTA of four warps owns 16, 32 or 64 query rows: the heads of one token (blocks of heads when there are more; several consecutive
+// A CTA of eight warps owns 16, 32 or 64 query rows: the heads of one token (blocks of heads when there are more; several consecutive
 // tokens of one request when a prompt portion has them), and walks the keys they see in tiles of 64, which all its rows
 // share: a cached row is read once for all of them (with 16 rows the kernel is bound by the key tiles' way from L2). Per tile:
-//   S = Q K^T   warp w takes keys 16w..16w+15 over the whole row (m16n8k16, float32 accumulators), scales and masks them,
-//               and the four warps exchange row maxima and row sums through shared memory;
+//   S = Q K^T   warp w takes keys 8w..8w+7 over the whole row (m16n8k16, float32 accumulators), scales and masks them,
+//               and the warps exchange row maxima and row sums through shared memory;
 //   P           float32 weights exp(s - m), rounded to bfloat16 only as the operand of the second product; the sums l use
 //               the float32 values;
-//   O += P C    warp w takes the latent's 16-value chunks w, w + 4, ... of all 64 keys.
+//   O += P C    warp w takes the latent's 16-value chunks w, w + 8, ... of all 64 keys.
 // Key tiles are copied with 16-byte cp.async through the block table into two swizzled buffers (the next tile arrives while
 // this one is used); rows past the last visible key are zero-filled. With slices (steps of single decoded tokens), a CTA
 // takes one slice of the keys and writes unnormalised partial results that latent_combine merges.
@@ -21,9 +21,10 @@
 namespace {
 
 constexpr int kKeys = 64;    // keys of a tile
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;
+constexpr int kKeysPerWarp = kKeys / kWarps;   // 8: one n-tile of the S product a warp
 
-// NCH: 16-value chunks of the latent a warp owns at most (rank <= 64 * NCH). MT: 16-row tiles of queries a CTA holds.
+// NCH: 16-value chunks of the latent a warp owns at most (rank <= 16 * kWarps * NCH). MT: 16-row tiles of queries a CTA holds.
 template <int NCH, int MT>
 __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const float* __restrict__ q, IbKvView kv, const int* __restrict__ positions,
                                                                            const int* __restrict__ seg_of_token, const int2* __restrict__ units, float scale,
@@ -36,8 +37,8 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
   const uint32_t s_k = mt::smem_u32(smem);                   // two key tiles
   const uint32_t s_q = s_k + 2 * k_bytes;                    // [R][D]
   const uint32_t s_p = s_q + (uint32_t)blocks * R * 128;     // [R][64]
-  float* wmax = (float*)(smem + 2 * k_bytes + (size_t)blocks * R * 128 + R * 128);   // [4][R]
-  float* wsum = wmax + kWarps * R;                                                   // [4][R]
+  float* wmax = (float*)(smem + 2 * k_bytes + (size_t)blocks * R * 128 + R * 128);   // [warps][R]
+  float* wsum = wmax + kWarps * R;                                                   // [warps][R]
   ib::pdl_launch_dependents();
   ib::pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
@@ -80,25 +81,53 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(s_q + mt::tile_offset<64, R>(r, c)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
   }
   const __nv_bfloat16* base = (const __nv_bfloat16*)kv.base;
-  // eight threads copy one row's 128-byte pieces; sixteen rows a pass
-  auto issue_tile = [&](int k0, int buf) {
-    const uint32_t dst = s_k + buf * k_bytes;
+  // eight threads copy one row's 128-byte pieces; 32 rows a pass. What a thread's addresses share is computed once: a warp is
+  // alone on its scheduler here, and every instruction that is not a product or a copy is time.
+  const int r7 = lane & 7;
+  const uint32_t cp_off = (uint32_t)((tid >> 3) * 128 + (((tid & 7) ^ ((tid >> 3) & 7)) << 4));
+  const int cp_iters = (D / 8 - (tid & 7) + 7) / 8;
+  // The rows' places in the pool (a look-up in the block table each: a trip to memory) are fetched one tile ahead of the copies
+  // that use them, so that no warp waits for them between a barrier and its products.
+  constexpr int kPasses = kKeys / (kWarps * 4);
+  long long off[kPasses];
+  auto look_up = [&](int k0) {
 #pragma unroll
-    for (int pass = 0; pass < kKeys / 16; pass++) {
-      const int r = pass * 16 + (tid >> 3), key = k0 + r;
-      long long off = -1;
+    for (int pass = 0; pass < kPasses; pass++) {
+      const int key = k0 + pass * (kWarps * 4) + (tid >> 3);
+      off[pass] = -1;
       if (key <= hi) {
-        off = ib::kv_offset(kv, seg, key, 0);
-        if (off < 0) atomicOr(status, IB_ERR_BAD_PAGE);
+        off[pass] = ib::kv_offset(kv, seg, key, 0);
+        if (off[pass] < 0) atomicOr(status, IB_ERR_BAD_PAGE);
       }
-      for (int c = tid & 7; c < D / 8; c += 8) {
-        const uint32_t at = dst + mt::tile_offset<64, kKeys>(r, c);
-        if (off >= 0) mt::cp_async16(at, base + off + c * 8);
-        else mt::st_shared_zero16(at);
+    }
+  };
+  auto issue_tile = [&](int buf) {   // the tile whose rows `off` holds
+    const uint32_t dst = s_k + buf * k_bytes + cp_off;
+#pragma unroll
+    for (int pass = 0; pass < kPasses; pass++) {
+      const __nv_bfloat16* src = base + off[pass] + (tid & 7) * 8;
+      uint32_t at = dst + pass * (kWarps * 4 * 128);
+      if (off[pass] >= 0) {
+        for (int it = 0; it < cp_iters; it++, at += kKeys * 128, src += 64) mt::cp_async16(at, src);
+      } else {
+        for (int it = 0; it < cp_iters; it++, at += kKeys * 128) mt::st_shared_zero16(at);
       }
     }
     mt::cp_async_commit();
   };
+  // fragment addresses: a fragment row's low three bits are the lane's, so the swizzle of the four 16-value steps of a 64-value block
+  // is four constants a thread; a block further on is a fixed stride
+  const int hb = lane >> 4, mb = (lane >> 3) & 1;
+  const uint32_t a_row_off = (uint32_t)((r7 + 8 * mb) * 128);           // Q, P and V fragments: row (lane & 7) + 8 * ((lane >> 3) & 1) of their 16
+  const uint32_t k_row_off = (uint32_t)((kKeysPerWarp * warp + r7) * 128);   // K fragments: this warp's 8 keys (lanes 0-15 give the addresses)
+  uint32_t sw_a[4], sw_k[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    sw_a[j] = (uint32_t)(((2 * j + hb) ^ r7) << 4);
+    sw_k[j] = (uint32_t)(((2 * j + mb) ^ r7) << 4);
+  }
+  // V fragments: chunk 2 (warp + 8 i) + hb = block 2 i + (2 warp + hb) / 8, place (2 warp + hb) % 8
+  const uint32_t v_off = a_row_off + (uint32_t)(((2 * warp + hb) >> 3) * kKeys * 128 + ((((2 * warp + hb) & 7) ^ r7) << 4));
   float o[MT][NCH][2][4];
   float m[MT][2], l[MT][2];
 #pragma unroll
@@ -113,45 +142,53 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
         for (int e = 0; e < 4; e++) o[a][i][n][e] = 0.f;
   }
   const int n_tiles = hi >= lo ? (hi - lo) / kKeys + 1 : 0;
-  if (n_tiles > 0) issue_tile(lo, 0);
+  if (n_tiles > 0) {
+    look_up(lo);
+    issue_tile(0);
+    if (n_tiles > 1) look_up(lo + kKeys);
+  }
   for (int j = 0; j < n_tiles; j++) {
     const int k0 = lo + j * kKeys, buf = j & 1;
     mt::cp_async_wait<0>();
     __syncthreads();                                       // tile j is here; everybody is done with tile j - 1 and with P
-    if (j + 1 < n_tiles) issue_tile(k0 + kKeys, buf ^ 1);
+    if (j + 1 < n_tiles) {
+      issue_tile(buf ^ 1);
+      if (j + 2 < n_tiles) look_up(k0 + 2 * kKeys);
+    }
     const uint32_t kt = s_k + buf * k_bytes;
-    // ---- S: this warp's 16 keys, every row tile
-    float s[MT][2][4];
+    // ---- S: this warp's 8 keys, every row tile
+    float s[MT][4];
 #pragma unroll
     for (int a = 0; a < MT; a++)
 #pragma unroll
-      for (int n = 0; n < 2; n++)
+      for (int e = 0; e < 4; e++) s[a][e] = 0.f;
+    {
+      const int ksteps = D / 16;
+      uint32_t ka = kt + k_row_off, qa = s_q + a_row_off;
+      for (int kk0 = 0; kk0 < ksteps; kk0 += 4, ka += kKeys * 128, qa += R * 128) {
 #pragma unroll
-        for (int e = 0; e < 4; e++) s[a][n][e] = 0.f;
-#pragma unroll 2
-    for (int kk = 0; kk < D / 16; kk++) {
-      uint32_t r[4];
-      mt::load_k_frag<64, kKeys>(kt, 16 * warp, kk, lane, r);
+        for (int j = 0; j < 4; j++) {
+          if (kk0 + j < ksteps) {   // only the last block of a row may be partial
+            uint32_t b0, b1, fa[MT][4];
+            asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(ka + sw_k[j]));
 #pragma unroll
-      for (int a = 0; a < MT; a++) {
-        uint32_t fa[4];
-        mt::load_a_frag<64, R>(s_q, 16 * a, kk, lane, fa);
-        mt::mma_16816(s[a][0], fa, r[0], r[1]);
-        mt::mma_16816(s[a][1], fa, r[2], r[3]);
+            for (int a = 0; a < MT; a++) mt::ldmatrix_x4(qa + a * 2048 + sw_a[j], fa[a][0], fa[a][1], fa[a][2], fa[a][3]);
+#pragma unroll
+            for (int a = 0; a < MT; a++) mt::mma_16816(s[a], fa[a], b0, b1);
+          }
+        }
       }
     }
 #pragma unroll
     for (int a = 0; a < MT; a++) {
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int n = 0; n < 2; n++)
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const int key = k0 + 16 * warp + 8 * n + 2 * t4 + (e & 1), rr = e >> 1;
-          const float v = (key <= hi && key <= row_pos[a][rr]) ? s[a][n][e] * scale : -INFINITY;
-          s[a][n][e] = v;
-          mx[rr] = fmaxf(mx[rr], v);
-        }
+      for (int e = 0; e < 4; e++) {
+        const int key = k0 + kKeysPerWarp * warp + 2 * t4 + (e & 1), rr = e >> 1;
+        const float v = (key <= hi && key <= row_pos[a][rr]) ? s[a][e] * scale : -INFINITY;
+        s[a][e] = v;
+        mx[rr] = fmaxf(mx[rr], v);
+      }
 #pragma unroll
       for (int rr = 0; rr < 2; rr++) {
         mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
@@ -167,25 +204,24 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
 #pragma unroll
       for (int rr = 0; rr < 2; rr++) {
         const int r = 16 * a + g + 8 * rr;
-        const float mt_ = fmaxf(fmaxf(wmax[r], wmax[R + r]), fmaxf(wmax[2 * R + r], wmax[3 * R + r]));
+        float mt_ = wmax[r];
+#pragma unroll
+        for (int w = 1; w < kWarps; w++) mt_ = fmaxf(mt_, wmax[w * R + r]);
         const float m_new = fmaxf(m[a][rr], mt_);
         corr[a][rr] = m_new == -INFINITY ? 1.f : __expf(m[a][rr] - m_new);
         m[a][rr] = m_new;
         sum[rr] = 0.f;
       }
+      float p[4];
 #pragma unroll
-      for (int n = 0; n < 2; n++) {
-        float p[4];
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const int rr = e >> 1;
-          p[e] = s[a][n][e] == -INFINITY ? 0.f : __expf(s[a][n][e] - m[a][rr]);
-          sum[rr] += p[e];
-        }
-        const int chunk = 2 * warp + n;   // 8 keys a chunk
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_p + mt::tile_offset<64, R>(16 * a + g, chunk) + 4 * t4), "r"(mt::pack_bf16(p[0], p[1])) : "memory");
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_p + mt::tile_offset<64, R>(16 * a + g + 8, chunk) + 4 * t4), "r"(mt::pack_bf16(p[2], p[3])) : "memory");
+      for (int e = 0; e < 4; e++) {
+        const int rr = e >> 1;
+        p[e] = s[a][e] == -INFINITY ? 0.f : __expf(s[a][e] - m[a][rr]);
+        sum[rr] += p[e];
       }
+      // this warp's 8 keys are chunk `warp` of the P tile's 64
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_p + mt::tile_offset<64, R>(16 * a + g, warp) + 4 * t4), "r"(mt::pack_bf16(p[0], p[1])) : "memory");
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_p + mt::tile_offset<64, R>(16 * a + g + 8, warp) + 4 * t4), "r"(mt::pack_bf16(p[2], p[3])) : "memory");
 #pragma unroll
       for (int rr = 0; rr < 2; rr++) {
         sum[rr] += __shfl_xor_sync(0xffffffffu, sum[rr], 1);
@@ -199,7 +235,10 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
 #pragma unroll
       for (int rr = 0; rr < 2; rr++) {
         const int r = 16 * a + g + 8 * rr;
-        l[a][rr] = l[a][rr] * corr[a][rr] + ((wsum[r] + wsum[R + r]) + (wsum[2 * R + r] + wsum[3 * R + r]));
+        float t = wsum[r];
+#pragma unroll
+        for (int w = 1; w < kWarps; w++) t += wsum[w * R + r];
+        l[a][rr] = l[a][rr] * corr[a][rr] + t;
       }
 #pragma unroll
       for (int i = 0; i < NCH; i++)
@@ -209,22 +248,25 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
           o[a][i][n][2] *= corr[a][1], o[a][i][n][3] *= corr[a][1];
         }
     }
-    // ---- O += P C: this warp's chunks of the latent
+    // ---- O += P C: this warp's chunks of the latent; the next chunk's fragment is requested before this one's products
 #pragma unroll
     for (int ks = 0; ks < kKeys / 16; ks++) {
       uint32_t fa[MT][4];
 #pragma unroll
-      for (int a = 0; a < MT; a++) mt::load_a_frag<64, R>(s_p, 16 * a, ks, lane, fa[a]);
+      for (int a = 0; a < MT; a++) mt::ldmatrix_x4(s_p + a_row_off + a * 2048 + sw_a[ks], fa[a][0], fa[a][1], fa[a][2], fa[a][3]);
+      const uint32_t va = kt + v_off + ks * 2048;
+      uint32_t r[2][4];
+      if (warp * 16 < rank) mt::ldmatrix_x4_trans(va, r[0][0], r[0][1], r[0][2], r[0][3]);
 #pragma unroll
       for (int i = 0; i < NCH; i++) {
         const int dp = warp + kWarps * i;
+        if (i + 1 < NCH && (dp + kWarps) * 16 < rank)
+          mt::ldmatrix_x4_trans(va + (i + 1) * (kWarps / 4) * kKeys * 128, r[(i + 1) & 1][0], r[(i + 1) & 1][1], r[(i + 1) & 1][2], r[(i + 1) & 1][3]);
         if (dp * 16 < rank) {
-          uint32_t r[4];
-          mt::load_v_frag<64, kKeys>(kt, 16 * ks, dp, lane, r);
 #pragma unroll
           for (int a = 0; a < MT; a++) {
-            mt::mma_16816(o[a][i][0], fa[a], r[0], r[1]);
-            mt::mma_16816(o[a][i][1], fa[a], r[2], r[3]);
+            mt::mma_16816(o[a][i][0], fa[a], r[i & 1][0], r[i & 1][1]);
+            mt::mma_16816(o[a][i][1], fa[a], r[i & 1][2], r[i & 1][3]);
           }
         }
       }
@@ -284,6 +326,8 @@ extern "C" int ib_latent_attention_mma_supports(int rank, int D) { return rank >
 extern "C" int ib_latent_attention_mma_rows(int rank, int D, int rows_wanted) {
   int mt = rank > 256 ? 2 : 4;
   while (mt > 1 && (16 * (mt / 2) >= rows_wanted || latent_mma_smem(D, mt) > 200 * 1024)) mt /= 2;
+  // two CTAs an SM beat one with twice the rows (measured: 8 heads of 256 + 32, 2,048 tokens: 154 against 197 us), where halving makes room for two
+  if (mt > 1 && 16 * (mt / 2) < rows_wanted && latent_mma_smem(D, mt) > 110 * 1024 && latent_mma_smem(D, mt / 2) <= 110 * 1024) mt /= 2;
   return 16 * mt;
 }
 
@@ -314,12 +358,11 @@ extern "C" int ib_latent_attention_mma(const float* q, const IbKvView* kv, const
     constexpr int NCH = decltype(nch)::value;
     if (mt == 1) go(latent_attention_mma_kernel<NCH, 1>);
     else if (mt == 2) go(latent_attention_mma_kernel<NCH, 2>);
-    else if constexpr (NCH <= 4) go(latent_attention_mma_kernel<NCH, 4>);
+    else if constexpr (NCH <= 2) go(latent_attention_mma_kernel<NCH, 4>);
   };
-  if (rank <= 64) pick(std::integral_constant<int, 1>());
-  else if (rank <= 128) pick(std::integral_constant<int, 2>());
-  else if (rank <= 256) pick(std::integral_constant<int, 4>());
-  else pick(std::integral_constant<int, 8>());
+  if (rank <= 128) pick(std::integral_constant<int, 1>());
+  else if (rank <= 256) pick(std::integral_constant<int, 2>());
+  else pick(std::integral_constant<int, 4>());
   IB_CHECK_LAUNCH("latent_attention_mma");
   if (n_slices > 1) return ib_latent_combine(part_o, part_ml, out, IB_BF16, T * heads, rank, n_slices, stream);
   return 0;
