@@ -408,3 +408,53 @@ def test_generation_in_bfloat16_runs_and_long_decoding_stays_close(zdirs):
     for i, tok in enumerate(got):
         row = lg[len(prompt) + i - 1]
         assert row[tok] >= row.max() - 0.25, f"decoded token {i}: the plain model's logit for it is {row.max() - row[tok]:.3f} below its best"
+
+
+# ------------------------------------------------------------------------------------------ the programs a user runs
+def test_trace_replay_program_and_command_line(zdirs, tmp_path):
+    """bin/trace_run as a subprocess fed JSON steps (a mixed trace, bfloat16), and `run`, `batch` and `spec` of the command line, on a
+    model folder of this architecture: nothing in them names an architecture."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    name = "R"
+    vocab = tz.CONFIGS[name]["config"]["vocab"]
+    reqs = {r: traces.prompt(900 + i, n, vocab) for i, (r, n) in enumerate({"a": 70, "b": 9, "c": 33, "d": 64, "e": 2}.items())}
+    steps = traces.mixed(reqs, seed=5)
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(zdirs[name]), "--dtype", "bfloat16", "--out", str(out),
+                           "--max-tokens", str(traces.max_live_tokens(steps)), "--page-size", "32"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    plain = P.PlainZabonex(zdirs[name])
+    want = {r: plain.logits(t).numpy() for r, t in reqs.items()}
+    at, over, n_rows = {r: 0 for r in reqs}, 0, 0
+    for s in steps:
+        rows = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab)
+        k = 0
+        for e in s["entries"]:
+            for w in e["want"]:
+                err = np.abs(rows[k] - want[e["id"]][at[e["id"]] + w]).max() / np.abs(want[e["id"]]).max()
+                assert err <= BF16_WORST
+                over += err > TOLERANCE["bfloat16"]
+                k += 1
+            at[e["id"]] += len(e["tokens"])
+        assert k == rows.shape[0]
+        n_rows += k
+    assert over <= max(3, BF16_ROWS_OVER * n_rows)
+    env = dict(os.environ, PYTHONPATH=root)
+    p = subprocess.run([sys.executable, "-m", "inference_bench_b200", "run", "--model", str(zdirs[name]), "--prompt-len", "12", "--max-tokens", "5", "--json",
+                        "--dtype", "float32", "--max-ctx", "64"], capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    r = json.loads(p.stdout)
+    from inference_bench_b200.cli import _synthetic_prompt
+    assert r["prompt_tokens"] == 12 and r["tokens"] == plain.greedy(_synthetic_prompt(12, vocab), 5)
+    p = subprocess.run([sys.executable, "-m", "inference_bench_b200", "batch", "--model", str(zdirs[name]), "--sizes", "1,3", "--prompt-len", "20", "--max-tokens", "6",
+                        "--json", "--max-ctx", "64"], capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [b["completion_tokens"] for b in json.loads(p.stdout)] == [6, 18]
+    p = subprocess.run([sys.executable, "-m", "inference_bench_b200", "spec", "--model", str(zdirs[name])], capture_output=True, text=True, env=env)
+    assert p.returncode == 0 and json.loads(p.stdout)["layers"][1]["mixer"]["kv_from"] == 0
