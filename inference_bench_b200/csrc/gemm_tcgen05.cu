@@ -422,12 +422,13 @@ extern "C" int ib_gemm_grouped_tcgen05(const void* x, const void* w, float* out,
     case 32: return launch<32, 1, EPI_STORE>(tw, tx, out, R, N, K, 1, total_kt, 0, status, stream, 0, g);
     case 64: return launch<64, 1, EPI_STORE>(tw, tx, out, R, N, K, 1, total_kt, 0, status, stream, 0, g);
     case 128: return launch<128, 1, EPI_STORE>(tw, tx, out, R, N, K, 1, total_kt, 0, status, stream, 0, g);
-    default: return ib_set_error("gemm_grouped_tcgen05: token tile %d is not one of 16, 32, 64, 128", bn);
+    case 256: return launch<256, 1, EPI_STORE>(tw, tx, out, R, N, K, 1, total_kt, 0, status, stream, 0, g);
+    default: return ib_set_error("gemm_grouped_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", bn);
   }
 }
 
 // w [E, 2 I, K]: every expert's gate rows then its up rows; act [R, I] bfloat16 = silu(x gate^T) * (x up^T) per expert.
-// bn 16 or 32: 64 gate rows and their up rows in one accumulator (I a multiple of 64); bn 64 or 128: two accumulators.
+// bn 16 or 32: 64 gate rows and their up rows in one accumulator (I a multiple of 64); bn 64, 128 or 256: two accumulators.
 extern "C" int ib_gemm_grouped_swiglu_tcgen05(const void* x, const void* w, void* act, int R, int I, int K, int bn, const int* offsets, const int* tiles, int E,
                                               unsigned* status, cudaStream_t stream) {
   if (R == 0 || I == 0) return 0;
@@ -448,6 +449,7 @@ extern "C" int ib_gemm_grouped_swiglu_tcgen05(const void* x, const void* w, void
   switch (bn) {
     case 64: return launch<64, 2, EPI_SWIGLU>(tw, tx, act, R, I, K, 1, total_kt, I, status, stream, 0, g);
     case 128: return launch<128, 2, EPI_SWIGLU>(tw, tx, act, R, I, K, 1, total_kt, I, status, stream, 0, g);
-    default: return ib_set_error("gemm_grouped_swiglu_tcgen05: token tile %d is not one of 16, 32, 64, 128", bn);
+    case 256: return launch<256, 2, EPI_SWIGLU>(tw, tx, act, R, I, K, 1, total_kt, I, status, stream, 0, g);
+    default: return ib_set_error("gemm_grouped_swiglu_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", bn);
   }
 }

@@ -62,7 +62,7 @@ class RoutedExperts(base.FeedForward):
         offsets, tile_start = rt.empty((E + 1,), torch.int32), rt.empty((E + 1,), torch.int32)
         row_of_pair, token_of_row = rt.empty((R,), torch.int32), rt.empty((R,), torch.int32)
         how = rt.options.expert_gemm
-        bn = G.grouped_token_tile(R, E)
+        bn = G.grouped_token_tile(R, E, self.expert_ff, rt.sm_count)
         act = rt.empty((R, self.expert_ff))
         y = rt.empty((R, self.hidden), torch.float32)
         if how in ("auto", "tcgen05") and rt.act_dtype == torch.bfloat16 and rt.gemm != "simt" and G.grouped_supported(self.hidden, self.expert_ff, bn):

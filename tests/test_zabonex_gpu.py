@@ -255,7 +255,7 @@ def test_experts_on_regrouped_rows(rt32, T, E, top, W, F):
         assert torch.allclose(out.cpu().double(), want16, atol=2e-3)
         # and on tcgen05: the rows gathered into the experts' order first, token tiles of every size the kernel has
         from inference_bench_b200.kernels import gemm_tcgen05 as G
-        for bn in (16, 32, 64, 128):
+        for bn in (16, 32, 64, 128, 256):
             if not G.grouped_supported(W, F, bn):
                 continue
             ops.moe_sort(idx_d, E, offsets, tile_start, row_of_pair, token_of_row, tile_rows=bn)
