@@ -26,7 +26,7 @@ import ctypes as C
 
 import numpy as np
 
-from ..parts.base import FixedState, PagedKV, PagedRows
+from ..parts.base import FixedState, PagedKV, PagedRows, Several
 from . import native
 from .pages import PagePool
 
@@ -89,7 +89,7 @@ class StateView:
 class CacheManager:
     def __init__(self, needs: Sequence[Any], page_size: int, num_pages: int, max_requests: int, max_tokens_per_request: int,
                  device=None, dtype=None, sources: Optional[Sequence[int]] = None):
-        """needs[i]: PagedKV, FixedState or None for schedule entry i; sources[i]: the entry whose
+        """needs[i]: PagedKV, PagedRows, FixedState, Several (a tuple of those) or None for schedule entry i; sources[i]: the entry whose
         cache entry i uses (itself by default). num_pages: pages of every group's pool."""
         if page_size <= 0 or max_requests <= 0 or max_tokens_per_request <= 0:
             raise ValueError("page_size, max_requests and max_tokens_per_request must be positive")
@@ -103,19 +103,28 @@ class CacheManager:
         self.place: dict[int, tuple[int, int]] = {}    # schedule entry -> (group index, index inside the page)
         self.states: dict[int, StateView] = {}         # schedule entry -> fixed state
         by_need: dict[Any, int] = {}
+        self._fixed: dict[Any, FixedState] = {}
+        self._several: dict[int, int] = {}             # schedule entry -> how many things it asked for (`Several`)
+        # a single need of entry i is known as i; item k of a `Several` as (i, k)
         for i, need in enumerate(needs):
-            if isinstance(need, (PagedKV, PagedRows)):
-                g = by_need.get(need)
-                if g is None:
-                    g = by_need[need] = len(self.groups)
-                    self.groups.append(Group(need, [], None))
-                self.place[i] = (g, len(self.groups[g].entries))
-                self.groups[g].entries.append(i)
-            elif isinstance(need, FixedState):
-                self.states[i] = StateView(None)
-            elif need is not None:
-                raise TypeError(f"schedule entry {i} asks the cache for {need!r}, which it does not know")
-        self._fixed = {i: n for i, n in enumerate(needs) if isinstance(n, FixedState)}
+            if isinstance(need, Several):
+                self._several[i] = len(need.needs)
+                items = [((i, k), n) for k, n in enumerate(need.needs)]
+            else:
+                items = [(i, need)]
+            for key, n in items:
+                if isinstance(n, (PagedKV, PagedRows)):
+                    g = by_need.get(n)
+                    if g is None:
+                        g = by_need[n] = len(self.groups)
+                        self.groups.append(Group(n, [], None))
+                    self.place[key] = (g, len(self.groups[g].entries))
+                    self.groups[g].entries.append(i)
+                elif isinstance(n, FixedState):
+                    self.states[key] = StateView(None)
+                    self._fixed[key] = n
+                elif n is not None:
+                    raise TypeError(f"schedule entry {i} asks the cache for {n!r}, which it does not know")
         self._lib = native.load()
         windows = (C.c_int * max(1, len(self.groups)))(*[int(g.need.window or 0) for g in self.groups])
         self._core = self._lib.ibh_cache_new(len(self.groups), windows, page_size, num_pages, max_requests, max_tokens_per_request)
@@ -270,16 +279,14 @@ class CacheManager:
         """Per schedule entry, what its mixer gets this step: a KvLayerView on its group's tensor
         (its own place in the page, or that of the entry whose cache it reads), a StateView, or None."""
         from ..kernels.ops import KvLayerView
-        out = []
-        for i, src in enumerate(self.sources):
-            if src in self.place:
-                g, e = self.place[src]
-                out.append(KvLayerView(self.groups[g].tensor, e, device_tables[g]))
-            elif src in self.states:
-                out.append(self.states[src])
-            else:
-                out.append(None)
-        return out
+
+        def one(key):
+            if key in self.place:
+                g, e = self.place[key]
+                return KvLayerView(self.groups[g].tensor, e, device_tables[g])
+            return self.states.get(key)
+
+        return [tuple(one((src, k)) for k in range(self._several[src])) if src in self._several else one(src) for src in self.sources]
 
     # ------------------------------------------------------------------ invariants
     def check(self) -> None:

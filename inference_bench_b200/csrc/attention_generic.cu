@@ -23,25 +23,30 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, int P, siz
                                        const float* __restrict__ k_norm_w, float eps, const float* __restrict__ cos_t,
                                        const float* __restrict__ sin_t, int rot_half, const int* __restrict__ positions,
                                        const int* __restrict__ seg_of_token, A* __restrict__ q_out, IbKvView kv, int write_kv, int T,
-                                       int heads, unsigned* __restrict__ status) {
+                                       int heads, unsigned* __restrict__ status, const float* __restrict__ bias, int qk_dim, int v_dim) {
+  // qk_dim, v_dim: sizes of a query/key head and of a value head (both at most the cache's row, kv.head_dim); the projection's row is
+  // [heads x qk_dim | kv_heads x qk_dim | kv_heads x v_dim]. bias: one value per entry of that row, or null.
   __shared__ float vec[kWarps][kMaxHeadDim];
   ib::pdl_launch_dependents();
   ib::pdl_wait();
-  const int hd = kv.head_dim, kvh = kv.kv_heads;
+  const int kvh = kv.kv_heads;
   const int slots = heads + 2 * kvh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   long long item = (long long)blockIdx.x * kWarps + warp;
   if (item >= (long long)T * slots) return;
   const int t = (int)(item / slots), j = (int)(item % slots);
-  const int R = slots * hd;
+  const int R = (heads + kvh) * qk_dim + kvh * v_dim;
   const bool is_q = j < heads, is_k = !is_q && j < heads + kvh;
   if (!is_q && !write_kv) return;
-  const float* src = qkv + (size_t)t * R + (size_t)j * hd;
+  const int hd = (is_q || is_k) ? qk_dim : v_dim;
+  const int col0 = (is_q || is_k) ? j * qk_dim : (heads + kvh) * qk_dim + (j - heads - kvh) * v_dim;
+  const float* src = qkv + (size_t)t * R + col0;
   float* v = vec[warp];
   float ss = 0.f;
   for (int d = lane; d < hd; d += 32) {
     float a = src[d];
     for (int p = 1; p < P; p++) a += src[p * stride_p + d];
+    if (bias) a += bias[col0 + d];
     v[d] = a;
     ss += a * a;
   }
@@ -86,7 +91,7 @@ __global__ void qk_norm_rope_kv_vec_kernel(const float* __restrict__ qkv, int P,
                                            const float* __restrict__ k_norm_w, float eps, const float* __restrict__ cos_t,
                                            const float* __restrict__ sin_t, const int* __restrict__ positions,
                                            const int* __restrict__ seg_of_token, A* __restrict__ q_out, IbKvView kv, int write_kv, int T,
-                                           int heads, unsigned* __restrict__ status) {
+                                           int heads, unsigned* __restrict__ status, const float* __restrict__ bias) {
   // blockIdx.x is the token; a warp takes PER consecutive heads of it (q heads, then k heads, then v heads)
   // and loads them all before it works on any: with many tokens (PER = 4) that keeps four loads per lane
   // in flight; with few, PER = 1 keeps the chain short. No division anywhere: this kernel is bound by
@@ -133,6 +138,10 @@ __global__ void qk_norm_rope_kv_vec_kernel(const float* __restrict__ qkv, int P,
         const float2 a = *(const float2*)(src + p * stride_p);
         v[u][0] += a.x, v[u][1] += a.y;
       }
+    }
+    if (bias) {
+#pragma unroll
+      for (int e = 0; e < E; e++) v[u][e] += bias[(size_t)j * HD + lane * E + e];
     }
   }
   if (cos_t && lane < 16) {   // (used only now, so that nothing waited for it above)
@@ -194,11 +203,13 @@ __global__ void qk_norm_rope_kv_vec_kernel(const float* __restrict__ qkv, int P,
 template <typename A, typename C>
 __global__ void attention_generic_kernel(const A* __restrict__ q, IbKvView kv, const int* __restrict__ positions,
                                          const int* __restrict__ seg_of_token, int window, float scale, A* __restrict__ out, int T,
-                                         int heads, unsigned* __restrict__ status) {
+                                         int heads, unsigned* __restrict__ status, int qk_dim, int v_dim, float softcap, int sink) {
+  // qk_dim, v_dim: a query/key head's and a value head's size (at most the cache's row). softcap > 0: s <- softcap * tanh(s / softcap).
+  // sink: the softmax has one more term whose score is 0 and which has no value (its denominator is 1 + sum exp(s)).
   __shared__ float qs[kWarps][kMaxHeadDim];
   ib::pdl_launch_dependents();
   ib::pdl_wait();
-  const int hd = kv.head_dim;
+  const int hd = qk_dim, row = kv.head_dim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   long long item = (long long)blockIdx.x * kWarps + warp;
   if (item >= (long long)T * heads) return;
@@ -212,7 +223,8 @@ __global__ void attention_generic_kernel(const A* __restrict__ q, IbKvView kv, c
   float acc[kMaxHeadDim / 32];
 #pragma unroll
   for (int r = 0; r < kMaxHeadDim / 32; r++) acc[r] = 0.f;
-  float m = -INFINITY, l = 0.f;
+  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;   // the sink is a key of score 0: it starts the running maximum and sum
+  (void)row;
   const C* base = (const C*)kv.base;
   for (int k0 = lo; k0 <= pos; k0 += 32) {
     int key = k0 + lane;
@@ -227,6 +239,7 @@ __global__ void attention_generic_kernel(const A* __restrict__ q, IbKvView kv, c
         float dot = 0.f;
         for (int d = 0; d < hd; d++) dot += qs[warp][d] * ib::to_f32<C>(kr[d]);
         s = dot * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);
       }
     }
     float m_new = fmaxf(m, ib::warp_max(s));
@@ -245,17 +258,17 @@ __global__ void attention_generic_kernel(const A* __restrict__ q, IbKvView kv, c
 #pragma unroll
       for (int r = 0; r < kMaxHeadDim / 32; r++) {
         int d = lane + 32 * r;
-        if (d < hd) acc[r] += pj * ib::to_f32<C>(vr[d]);
+        if (d < v_dim) acc[r] += pj * ib::to_f32<C>(vr[d]);
       }
     }
     m = m_new;
   }
   float inv = l > 0.f ? 1.f / l : 0.f;
-  A* orow = out + (size_t)t * heads * hd + (size_t)h * hd;
+  A* orow = out + (size_t)t * heads * v_dim + (size_t)h * v_dim;
 #pragma unroll
   for (int r = 0; r < kMaxHeadDim / 32; r++) {
     int d = lane + 32 * r;
-    if (d < hd) orow[d] = ib::from_f32<A>(acc[r] * inv);
+    if (d < v_dim) orow[d] = ib::from_f32<A>(acc[r] * inv);
   }
 }
 
@@ -275,26 +288,29 @@ int check_view(const char* name, const IbKvView* kv, int heads) {
 extern "C" int ib_qk_norm_rope_kv(const float* qkv, int P, long long stride_p, const float* q_norm_w, const float* k_norm_w, float eps,
                                   const float* cos_t, const float* sin_t, int rot_half, const int* positions, const int* seg_of_token,
                                   void* q_out, int act_dtype, const IbKvView* kv, int write_kv, int T, int heads, unsigned* status,
-                                  cudaStream_t stream) {
+                                  const float* bias, int qk_dim, int v_dim, cudaStream_t stream) {
+  // qk_dim, v_dim: 0 = the cache's row size. bias: float32, one value per column of the projection, or null.
   if (T == 0) return 0;
   if (check_view("qk_norm_rope_kv", kv, heads)) return 1;
+  if (qk_dim <= 0) qk_dim = kv->head_dim;
+  if (v_dim <= 0) v_dim = kv->head_dim;
   IB_CHECK_ARG(P >= 1 && T > 0, "qk_norm_rope_kv: bad sizes T=%d P=%d", T, P);
-  IB_CHECK_ARG(rot_half >= 0 && 2 * rot_half <= kv->head_dim, "qk_norm_rope_kv: rotary size %d exceeds head_dim %d", 2 * rot_half,
-               kv->head_dim);
+  IB_CHECK_ARG(qk_dim <= kv->head_dim && v_dim <= kv->head_dim, "qk_norm_rope_kv: head sizes %d and %d exceed the cache's row of %d", qk_dim, v_dim, kv->head_dim);
+  IB_CHECK_ARG(rot_half >= 0 && 2 * rot_half <= qk_dim, "qk_norm_rope_kv: rotary size %d exceeds head_dim %d", 2 * rot_half, qk_dim);
   IB_CHECK_ARG((act_dtype == IB_F32 && kv->dtype == IB_F32) || (act_dtype == IB_BF16 && kv->dtype == IB_BF16),
                "qk_norm_rope_kv: activation dtype %d and cache dtype %d must match", act_dtype, kv->dtype);
   long long items = (long long)T * (heads + 2 * kv->kv_heads);
   unsigned blocks = (unsigned)((items + kWarps - 1) / kWarps);
   const int hd = kv->head_dim;
   const bool aligned = ((uintptr_t)qkv % 16 == 0) && (stride_p % 4 == 0) && ((uintptr_t)q_out % 16 == 0) && ((uintptr_t)kv->base % 16 == 0);
-  const bool vec = (hd == 64 || hd == 128) && (rot_half == 0 || 2 * rot_half == hd) && aligned;
+  const bool vec = (hd == 64 || hd == 128) && qk_dim == hd && v_dim == hd && (rot_half == 0 || 2 * rot_half == hd) && aligned;
   const float* cs = rot_half ? cos_t : nullptr;
   if (vec) {
     const int slots = heads + 2 * kv->kv_heads;
     auto go = [&](auto kernel, int per, auto* qo) {
       const dim3 grid((unsigned)T, (unsigned)((slots + kWarps * per - 1) / (kWarps * per)));
       ib::launch(kernel, grid, kWarps * 32, 0, stream, qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cs, sin_t, positions, seg_of_token, qo, *kv,
-                 write_kv, T, heads, status);
+                 write_kv, T, heads, status, bias);
     };
     const bool many = (long long)T * slots >= 8192;   // a prompt portion: four heads per warp; a few decoded tokens: one
     if (act_dtype == IB_F32 && hd == 128) {
@@ -314,29 +330,34 @@ extern "C" int ib_qk_norm_rope_kv(const float* qkv, int P, long long stride_p, c
   else if (act_dtype == IB_F32)
     ib::launch(qk_norm_rope_kv_kernel<float, float>, blocks, kWarps * 32, 0, stream, qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cos_t, sin_t,
                                                                             rot_half, positions, seg_of_token, (float*)q_out, *kv, write_kv,
-                                                                            T, heads, status);
+                                                                            T, heads, status, bias, qk_dim, v_dim);
   else
     ib::launch(qk_norm_rope_kv_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, kWarps * 32, 0, stream, 
         qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cos_t, sin_t, rot_half, positions, seg_of_token, (__nv_bfloat16*)q_out, *kv,
-        write_kv, T, heads, status);
+        write_kv, T, heads, status, bias, qk_dim, v_dim);
   IB_CHECK_LAUNCH("qk_norm_rope_kv");
   return 0;
 }
 
 extern "C" int ib_attention_generic(const void* q, int act_dtype, const IbKvView* kv, const int* positions, const int* seg_of_token,
-                                    int window, float scale, void* out, int T, int heads, unsigned* status, cudaStream_t stream) {
+                                    int window, float scale, void* out, int T, int heads, unsigned* status, int qk_dim, int v_dim, float softcap, int sink,
+                                    cudaStream_t stream) {
+  // qk_dim, v_dim: 0 = the cache's row size; softcap: 0 = scores as they are; sink: 1 = one added to the softmax's denominator.
   if (T == 0) return 0;
   if (check_view("attention_generic", kv, heads)) return 1;
+  if (qk_dim <= 0) qk_dim = kv->head_dim;
+  if (v_dim <= 0) v_dim = kv->head_dim;
+  IB_CHECK_ARG(qk_dim <= kv->head_dim && v_dim <= kv->head_dim, "attention_generic: head sizes %d and %d exceed the cache's row of %d", qk_dim, v_dim, kv->head_dim);
   IB_CHECK_ARG((act_dtype == IB_F32 && kv->dtype == IB_F32) || (act_dtype == IB_BF16 && kv->dtype == IB_BF16),
                "attention_generic: activation dtype %d and cache dtype %d must match", act_dtype, kv->dtype);
   long long items = (long long)T * heads;
   unsigned blocks = (unsigned)((items + kWarps - 1) / kWarps);
   if (act_dtype == IB_F32)
     ib::launch(attention_generic_kernel<float, float>, blocks, kWarps * 32, 0, stream, (const float*)q, *kv, positions, seg_of_token, window, scale,
-                                                                              (float*)out, T, heads, status);
+                                                                              (float*)out, T, heads, status, qk_dim, v_dim, softcap, sink);
   else
     ib::launch(attention_generic_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, kWarps * 32, 0, stream, 
-        (const __nv_bfloat16*)q, *kv, positions, seg_of_token, window, scale, (__nv_bfloat16*)out, T, heads, status);
+        (const __nv_bfloat16*)q, *kv, positions, seg_of_token, window, scale, (__nv_bfloat16*)out, T, heads, status, qk_dim, v_dim, softcap, sink);
   IB_CHECK_LAUNCH("attention_generic");
   return 0;
 }

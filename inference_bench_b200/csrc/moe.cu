@@ -1,7 +1,8 @@
 // Routed feed-forward (mixture of experts): the router's choice, the regrouping of the step's tokens by expert,
 // the experts' matrix products on the regrouped rows, and the weighted sum back into token order.
 //
-//  * moe_route: per token, s = softmax(router logits) over all experts in float32; experts lie in `n_groups` equal
+//  * moe_route: per token, s = softmax(router logits) over all experts in float32 (or, with `score` = 1, s = sigmoid of each logit
+//    on its own); experts lie in `n_groups` equal
 //    groups of neighbours, a group's score is its largest s, only the `keep` best groups stay eligible; the `top`
 //    eligible experts with the largest s are chosen (ties: the lower index), each weighted s * route_scale, or
 //    s / (sum of the chosen s) * route_scale with `renorm`.
@@ -10,7 +11,9 @@
 //  * gemm_grouped: out[r] = W[e(r)] x[src(r)] for every regrouped row r: a 64 x 64 tile belongs to one expert; float32
 //    FMA chains per output (a row's result does not depend on its place among the rows). With `gated`, W holds gate
 //    rows then up rows and the output is silu(gate) * up.
-//  * moe_combine: out[t] = sum_p base[p][t] + sum_k weight[t][k] * y[row(t, k)], in the order of the choices.
+//  * moe_combine: out[t] = sum_p base[p][t] + sum_k weight[t][k] * y[row(t, k)], in the order of the choices (without weights: the plain sum).
+//  * scatter_scaled_rows: out[row(t, k)] = weight[t][k] * x[t]: the step's rows in the experts' order with the router's weight on the
+//    expert's input (an expert is not linear, so a weight on its input is not one on its output).
 #include <type_traits>
 
 #include "common.cuh"
@@ -30,7 +33,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 }
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int P, size_t stride_p, int T, int E, int n_groups, int keep, int top, float route_scale,
-                                 int renorm, int* __restrict__ idx_out, float* __restrict__ wt_out) {
+                                 int renorm, int* __restrict__ idx_out, float* __restrict__ wt_out, int score) {
   extern __shared__ float sm[];   // per warp: E scores, then n_groups group scores
   ib::pdl_launch_dependents();
   ib::pdl_wait();
@@ -46,16 +49,20 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int P, size_t
     s[e] = z;
     mx = fmaxf(mx, z);
   }
-  mx = ib::warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    const float v = expf(s[e] - mx);
-    s[e] = v;
-    sum += v;
+  if (score == 1) {   // every expert's own sigmoid
+    for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-s[e]));
+  } else {
+    mx = ib::warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float v = expf(s[e] - mx);
+      s[e] = v;
+      sum += v;
+    }
+    sum = ib::warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < E; e += 32) s[e] *= inv;
   }
-  sum = ib::warp_sum(sum);
-  const float inv = 1.f / sum;
-  for (int e = lane; e < E; e += 32) s[e] *= inv;
   __syncwarp();
   if (n_groups > 1 && keep < n_groups) {
     const int per = E / n_groups;
@@ -254,22 +261,40 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) {
     float a = 0.f;
     for (int p = 0; p < P; p++) a += base[p * stride_p + (size_t)t * H + i];
-    for (int k = 0; k < top; k++) a = fmaf(wt[(size_t)t * top + k], y[(size_t)row_of_pair[(size_t)t * top + k] * H + i], a);
+    if (wt) {
+      for (int k = 0; k < top; k++) a = fmaf(wt[(size_t)t * top + k], y[(size_t)row_of_pair[(size_t)t * top + k] * H + i], a);
+    } else {
+      for (int k = 0; k < top; k++) a += y[(size_t)row_of_pair[(size_t)t * top + k] * H + i];
+    }
     out[(size_t)t * H + i] = a;
   }
+}
+
+// out[row_of_pair[p]] = wt[p] * x[p / top] for every (token, choice) pair p; the product is taken in float32 and rounded once.
+template <typename X>
+__global__ void scatter_scaled_rows_kernel(const X* __restrict__ x, const int* __restrict__ row_of_pair, const float* __restrict__ wt, int top, X* __restrict__ out,
+                                           int K) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int p = blockIdx.x;
+  const float c = wt[p];
+  const X* src = x + (size_t)(p / top) * K;
+  X* dst = out + (size_t)row_of_pair[p] * K;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < K; i += gridDim.y * blockDim.x) dst[i] = ib::from_f32<X>(c * ib::to_f32<X>(src[i]));
 }
 
 }  // namespace
 
 extern "C" int ib_moe_route(const float* logits, int P, long long stride_p, int T, int E, int n_groups, int keep, int top, float route_scale, int renorm,
-                            int* idx_out, float* wt_out, cudaStream_t stream) {
+                            int* idx_out, float* wt_out, int score, cudaStream_t stream) {
   if (T == 0) return 0;
   IB_CHECK_ARG(P >= 1 && E > 0 && top > 0 && top <= E, "moe_route: bad sizes P=%d experts=%d top=%d", P, E, top);
+  IB_CHECK_ARG(score == 0 || score == 1, "moe_route: score %d is neither 0 (softmax) nor 1 (sigmoid)", score);
   IB_CHECK_ARG(n_groups >= 1 && E % n_groups == 0 && keep >= 1 && keep <= n_groups, "moe_route: %d experts in %d groups of which %d stay", E, n_groups, keep);
   const size_t smem = (size_t)kRouteWarps * (E + n_groups) * sizeof(float);
   IB_CHECK_ARG(smem <= 48 * 1024, "moe_route: %d experts need %zu bytes of shared memory, more than 48 KiB", E, smem);
   ib::launch(moe_route_kernel, (unsigned)((T + kRouteWarps - 1) / kRouteWarps), kRouteWarps * 32, smem, stream, logits, P, (size_t)stride_p, T, E, n_groups, keep,
-             top, route_scale, renorm, idx_out, wt_out);
+             top, route_scale, renorm, idx_out, wt_out, score);
   IB_CHECK_LAUNCH("moe_route");
   return 0;
 }
@@ -323,5 +348,17 @@ extern "C" int ib_gather_rows(const void* x, const int* src_row, void* out, int 
   const int chunks = K * elem_bytes / 16;
   ib::launch(gather_rows_kernel, dim3(R, min((chunks + 127) / 128, 8)), 128, 0, stream, (const uint4*)x, src_row, (uint4*)out, chunks);
   IB_CHECK_LAUNCH("gather_rows");
+  return 0;
+}
+
+extern "C" int ib_scatter_scaled_rows(const void* x, int dtype, const int* row_of_pair, const float* wt, int top, void* out, int pairs, int K, cudaStream_t stream) {
+  if (pairs == 0) return 0;
+  IB_CHECK_ARG(pairs > 0 && K > 0 && top > 0, "scatter_scaled_rows: bad sizes pairs=%d K=%d top=%d", pairs, K, top);
+  const dim3 grid((unsigned)pairs, (unsigned)min((K + 255) / 256, 8));
+  if (dtype == IB_F32) ib::launch(scatter_scaled_rows_kernel<float>, grid, 256, 0, stream, (const float*)x, row_of_pair, wt, top, (float*)out, K);
+  else if (dtype == IB_BF16)
+    ib::launch(scatter_scaled_rows_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)x, row_of_pair, wt, top, (__nv_bfloat16*)out, K);
+  else return ib_set_error("scatter_scaled_rows: unknown dtype %d", dtype);
+  IB_CHECK_LAUNCH("scatter_scaled_rows");
   return 0;
 }

@@ -18,6 +18,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..config.runtime_options import RuntimeOptions
 from ..config.spec import ModelSpec, resolve_model
+from ..parts.base import flat_needs
 from ..sampling.params import GREEDY, SamplingParams
 from .executor import GpuExecutor
 from .model import load_model, random_model
@@ -78,7 +79,7 @@ class Engine:
         self.max_ctx = min(max_ctx or DEFAULT_MAX_CTX, limit)   # crates/specrt/src/engine.rs:53-60
         needs = self.decoder.cache_needs()
         if num_pages is None:
-            per_token = sum(2 * n.kv_heads * n.head_dim if hasattr(n, "kv_heads") else getattr(n, "width", 0) for n in needs if n is not None and not hasattr(n, "shape"))
+            per_token = sum(2 * n.kv_heads * n.head_dim if hasattr(n, "kv_heads") else getattr(n, "width", 0) for n in flat_needs(needs) if not hasattr(n, "shape"))
             per_page = per_token * page_size * torch.empty(0, dtype=self.rt.act_dtype).element_size()
             want = max_num_seqs * -(-self.max_ctx // page_size)
             if opts.kv_gb is not None:

@@ -160,13 +160,17 @@ def decode_fused(ctx, qkv: torch.Tensor, q_norm_w, k_norm_w, eps: float, cos, si
     return out
 
 
-def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, window: Optional[int], scale: float) -> torch.Tensor:
-    """q [T, heads*hd] (activation dtype) -> attention output of the same shape and dtype."""
+def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, window: Optional[int], scale: float, qk_dim: Optional[int] = None,
+                    v_dim: Optional[int] = None, softcap: float = 0.0, sink: bool = False) -> torch.Tensor:
+    """q [T, heads * qk_dim] (activation dtype) -> attention output [T, heads * v_dim] of the same dtype. qk_dim, v_dim: the head sizes
+    (default: the cache's row); softcap > 0 caps the scores with a tanh; sink adds one to the softmax's denominator."""
     rt = ctx.rt
-    out = rt.empty(tuple(q.shape), q.dtype)
     view = cache.c_view()
-    if not has_tensor_core_kernel(q.dtype, view.head_dim, heads, view.kv_heads):
-        ops.attention_generic(q, cache, ctx.positions, ctx.seg_of_token, window, scale, out, heads, rt.status)
+    qk_dim, v_dim = qk_dim or view.head_dim, v_dim or view.head_dim
+    out = rt.empty((q.shape[0], heads * v_dim), q.dtype)
+    variant = softcap > 0 or sink or qk_dim != view.head_dim or v_dim != view.head_dim
+    if variant or not has_tensor_core_kernel(q.dtype, view.head_dim, heads, view.kv_heads):
+        ops.attention_generic(q, cache, ctx.positions, ctx.seg_of_token, window, scale, out, heads, rt.status, qk_dim, v_dim, softcap, sink)
         return out
     work = _work_lists(ctx)
     stream = ops._stream()

@@ -165,14 +165,20 @@ def silu_mul(gate_up: torch.Tensor, act: torch.Tensor) -> None:
 
 def qk_norm_rope_kv(qkv: torch.Tensor, q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
                     cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor, seg_of_token: torch.Tensor,
-                    q_out: torch.Tensor, kv: KvLayerView, heads: int, status: torch.Tensor, write_kv: bool = True) -> None:
-    """qkv float32 [P, T, (heads + 2 kv_heads) * hd] -> q_out [T, heads*hd] and the paged cache."""
+                    q_out: torch.Tensor, kv: KvLayerView, heads: int, status: torch.Tensor, write_kv: bool = True,
+                    bias: Optional[torch.Tensor] = None, qk_dim: Optional[int] = None, v_dim: Optional[int] = None) -> None:
+    """qkv float32 [P, T, (heads + kv_heads) * qk_dim + kv_heads * v_dim] -> q_out [T, heads * qk_dim] and the paged cache.
+    qk_dim, v_dim: a query/key head's and a value head's size (default: the cache's row; neither may exceed it). bias: float32, one
+    value per column of the projection, added to the summed partial products."""
     _check("qkv", qkv, torch.float32)
     P, T, R = qkv.shape
     view = kv.c_view()
-    if R != (heads + 2 * view.kv_heads) * view.head_dim:
-        raise L.KernelError(f"qkv has {R} columns, expected {(heads + 2 * view.kv_heads) * view.head_dim}")
-    _check("q_out", q_out, None, (T, heads * view.head_dim))
+    qk_dim, v_dim = qk_dim or view.head_dim, v_dim or view.head_dim
+    if R != (heads + view.kv_heads) * qk_dim + view.kv_heads * v_dim:
+        raise L.KernelError(f"qkv has {R} columns, expected {(heads + view.kv_heads) * qk_dim + view.kv_heads * v_dim}")
+    _check("q_out", q_out, None, (T, heads * qk_dim))
+    if bias is not None:
+        _check("bias", bias, torch.float32, (R,))
     _check("positions", positions, torch.int32, (T,))
     _check("seg_of_token", seg_of_token, torch.int32, (T,))
     rot_half = 0
@@ -185,19 +191,23 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_norm_w: Optional[torch.Tensor], k_norm_
             _check(name, w, torch.float32, (view.head_dim,))
     L.call("ib_qk_norm_rope_kv", qkv.data_ptr(), P, T * R, _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(cos), _ptr(sin), rot_half,
            positions.data_ptr(), seg_of_token.data_ptr(), q_out.data_ptr(), dtype_code(q_out.dtype), C.byref(view), 1 if write_kv else 0, T,
-           heads, status.data_ptr(), _stream())
+           heads, status.data_ptr(), _ptr(bias), qk_dim, v_dim, _stream())
 
 
 def attention_generic(q: torch.Tensor, kv: KvLayerView, positions: torch.Tensor, seg_of_token: torch.Tensor, window: Optional[int],
-                      scale: float, out: torch.Tensor, heads: int, status: torch.Tensor) -> None:
+                      scale: float, out: torch.Tensor, heads: int, status: torch.Tensor, qk_dim: Optional[int] = None, v_dim: Optional[int] = None,
+                      softcap: float = 0.0, sink: bool = False) -> None:
+    """softcap > 0: scores become softcap * tanh(score / softcap); sink: the softmax's denominator has one added (a key of score 0
+    without a value); qk_dim, v_dim: a query/key head's and a value head's size (default: the cache's row)."""
     view = kv.c_view()
     T = q.shape[0]
-    _check("q", q, None, (T, heads * view.head_dim))
-    _check("out", out, q.dtype, (T, heads * view.head_dim))
+    qk_dim, v_dim = qk_dim or view.head_dim, v_dim or view.head_dim
+    _check("q", q, None, (T, heads * qk_dim))
+    _check("out", out, q.dtype, (T, heads * v_dim))
     _check("positions", positions, torch.int32, (T,))
     _check("seg_of_token", seg_of_token, torch.int32, (T,))
     L.call("ib_attention_generic", q.data_ptr(), dtype_code(q.dtype), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(),
-           int(window or 0), float(scale), out.data_ptr(), T, heads, status.data_ptr(), _stream())
+           int(window or 0), float(scale), out.data_ptr(), T, heads, status.data_ptr(), qk_dim, v_dim, float(softcap or 0.0), 1 if sink else 0, _stream())
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -389,7 +399,8 @@ def latent_attention_mma(q_full: torch.Tensor, kv: KvLayerView, positions: torch
 
 
 # ---------------------------------------------------------------- routed experts (csrc/moe.cu)
-L.register("ib_moe_route", [L._p, L._i, L._ll, L._i, L._i, L._i, L._i, L._i, L._f, L._i, L._p, L._p, L._p])
+L.register("ib_moe_route", [L._p, L._i, L._ll, L._i, L._i, L._i, L._i, L._i, L._f, L._i, L._p, L._p, L._i, L._p])
+L.register("ib_scatter_scaled_rows", [L._p, L._i, L._p, L._p, L._i, L._p, L._i, L._i, L._p])
 L.register("ib_moe_sort", [L._p, L._i, L._i, L._i, L._i, L._p, L._p, L._p, L._p, L._p])
 L.register("ib_gather_rows", [L._p, L._p, L._p, L._i, L._i, L._i, L._p])
 
@@ -412,13 +423,17 @@ L.register("ib_gemm_grouped", [L._p, L._i, L._p, L._p, L._i, L._p, L._i, L._p, L
 L.register("ib_moe_combine", [L._p, L._p, L._p, L._i, L._p, L._i, L._ll, L._p, L._i, L._i, L._p])
 
 
-def moe_route(logits: torch.Tensor, n_groups: int, keep: int, top: int, route_scale: float, renorm: bool, idx: torch.Tensor, wt: torch.Tensor) -> None:
-    """logits float32 [P, T, E] (partial sums) -> idx int32 [T, top], wt float32 [T, top]."""
+def moe_route(logits: torch.Tensor, n_groups: int, keep: int, top: int, route_scale: float, renorm: bool, idx: torch.Tensor, wt: torch.Tensor,
+              score: str = "softmax") -> None:
+    """logits float32 [P, T, E] (partial sums) -> idx int32 [T, top], wt float32 [T, top]. score: "softmax" over all experts, or
+    "sigmoid" of every expert's logit on its own."""
+    if score not in ("softmax", "sigmoid"):
+        raise L.KernelError(f"moe_route: score {score!r} is not known (softmax, sigmoid)")
     _check("logits", logits, torch.float32)
     P, T, E = logits.shape
     _check("idx", idx, torch.int32, (T, top))
     _check("wt", wt, torch.float32, (T, top))
-    L.call("ib_moe_route", logits.data_ptr(), P, T * E, T, E, n_groups, keep, top, float(route_scale), 1 if renorm else 0, idx.data_ptr(), wt.data_ptr(), _stream())
+    L.call("ib_moe_route", logits.data_ptr(), P, T * E, T, E, n_groups, keep, top, float(route_scale), 1 if renorm else 0, idx.data_ptr(), wt.data_ptr(), 1 if score == "sigmoid" else 0, _stream())
 
 
 def moe_sort(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, tile_start: torch.Tensor, row_of_pair: torch.Tensor, token_of_row: torch.Tensor,
@@ -458,8 +473,20 @@ def gemm_grouped(x: torch.Tensor, src_row: Optional[torch.Tensor], w: torch.Tens
            offsets.data_ptr(), tile_start.data_ptr(), R, E, N, K, 1 if gated else 0, _stream())
 
 
-def moe_combine(y: torch.Tensor, row_of_pair: torch.Tensor, wt: torch.Tensor, base: Optional[torch.Tensor], out: torch.Tensor) -> None:
-    """out[t] = sum_p base[p][t] + sum_k wt[t, k] * y[row_of_pair[t * top + k]]; y float32 [R, H], base float32 [P, T, H] or None."""
+def scatter_scaled_rows(x: torch.Tensor, row_of_pair: torch.Tensor, wt: torch.Tensor, out: torch.Tensor) -> None:
+    """out[row_of_pair[t * top + k]] = wt[t, k] * x[t]: the step's rows in the experts' order, each scaled by its pair's weight."""
+    T, top = wt.shape
+    K = x.shape[1]
+    _check("x", x, out.dtype, (T, K))
+    _check("out", out, None, (T * top, K))
+    _check("row_of_pair", row_of_pair, torch.int32, (T * top,))
+    _check("wt", wt, torch.float32)
+    L.call("ib_scatter_scaled_rows", x.data_ptr(), dtype_code(x.dtype), row_of_pair.data_ptr(), wt.data_ptr(), top, out.data_ptr(), T * top, K, _stream())
+
+
+def moe_combine(y: torch.Tensor, row_of_pair: torch.Tensor, wt: torch.Tensor, base: Optional[torch.Tensor], out: torch.Tensor, weighted: bool = True) -> None:
+    """out[t] = sum_p base[p][t] + sum_k wt[t, k] * y[row_of_pair[t * top + k]]; y float32 [R, H], base float32 [P, T, H] or None.
+    weighted=False: the plain sum over a token's choices (wt gives the shape only)."""
     T, top = wt.shape
     H = y.shape[1]
     _check("y", y, torch.float32, (T * top, H))
@@ -470,4 +497,129 @@ def moe_combine(y: torch.Tensor, row_of_pair: torch.Tensor, wt: torch.Tensor, ba
         if base.dim() != 3 or tuple(base.shape[1:]) != (T, H):
             raise L.KernelError(f"moe_combine: base must be [P, {T}, {H}], got {tuple(base.shape)}")
         P = base.shape[0]
-    L.call("ib_moe_combine", y.data_ptr(), row_of_pair.data_ptr(), wt.data_ptr(), top, _ptr(base), P, T * H, out.data_ptr(), T, H, _stream())
+    L.call("ib_moe_combine", y.data_ptr(), row_of_pair.data_ptr(), wt.data_ptr() if weighted else None, top, _ptr(base), P, T * H, out.data_ptr(), T, H, _stream())
+
+
+# ---------------------------------------------------------------- layer norm, input convolution, depth average (csrc/layernorm.cu)
+L.register("ib_add_layernorm", [L._p, L._p, L._i, L._ll, L._p, L._p, L._p, L._p, L._i, L._p, L._i, L._i, L._f, L._i, L._p, L._i, L._p, L._p, L._p, L._i, L._p, L._ll, L._p])
+L.register("ib_causal_conv_rows", [L._p, L._p, L._i, L._p, L._i, L._i, L._i, L._p, L._p, L._p, L._i, L._p, L._ll, L._p])
+L.register("ib_depth_average", [L._p, L._p, L._i, L._ll, L._p, L._p, L._p, L._ll, L._i, L._p, L._i, L._i, L._p])
+L.register("ib_scale_values", [L._p, L._ll, L._f, L._p])
+
+
+@dataclass
+class ConvLayout:
+    """Where `add_layernorm` puts its rows for the convolution over time that follows: every segment's rows preceded by `halo` rows
+    of the request's state (its last normed rows of earlier steps). state: float32 [slots, halo, H] (a view of one sublayer's part)."""
+    halo: int
+    seg_of_token: torch.Tensor
+    seg_start: torch.Tensor
+    seg_slot: torch.Tensor
+    n_segments: int
+    state: torch.Tensor
+    slot_stride: int        # float32 values between the states of consecutive slots
+
+    def rows(self, T: int) -> int:
+        return T + self.halo * self.n_segments
+
+
+def add_layernorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+                  delta_scale: Optional[torch.Tensor] = None, delta_bias: Optional[torch.Tensor] = None, x_copy: Optional[torch.Tensor] = None,
+                  layout: Optional[ConvLayout] = None) -> None:
+    """v = x + delta_scale * (sum_p delta[p] + delta_bias) (x updated in place unless `rows` gathers); x_copy = v (optional);
+    out = w * (v - mean) / sqrt(var + eps). With `layout` out is float32 [T + halo * segments, H] in the layout of `ConvLayout`."""
+    T, H = x.shape
+    _check("x", x, torch.float32)
+    _check("w", w, torch.float32, (H,))
+    n_rows = T if rows is None else rows.shape[0]
+    _check("out", out, torch.float32 if layout else None, (layout.rows(T) if layout else n_rows, H))
+    P, stride = 0, 0
+    if delta is not None:
+        _check("delta", delta, torch.float32)
+        if delta.dim() != 3 or tuple(delta.shape[1:]) != (T, H):
+            raise L.KernelError(f"delta must be [P, {T}, {H}], got {tuple(delta.shape)}")
+        P, stride = delta.shape[0], T * H
+    for name, v in (("delta_scale", delta_scale), ("delta_bias", delta_bias)):
+        if v is not None:
+            _check(name, v, torch.float32, (H,))
+    if x_copy is not None:
+        _check("x_copy", x_copy, torch.float32, (T, H))
+    if rows is not None:
+        _check("rows", rows, torch.int32)
+    lay = layout
+    L.call("ib_add_layernorm", x.data_ptr(), _ptr(delta), P, stride, _ptr(delta_scale), _ptr(delta_bias), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+           _ptr(rows), n_rows, H, float(eps), 0 if rows is not None else 1, _ptr(x_copy), lay.halo if lay else 0, _ptr(lay.seg_of_token) if lay else None,
+           _ptr(lay.seg_start) if lay else None, _ptr(lay.seg_slot) if lay else None, lay.n_segments if lay else 0, _ptr(lay.state) if lay else None,
+           lay.slot_stride if lay else 0, _stream())
+
+
+def causal_conv_rows(ext: torch.Tensor, w: torch.Tensor, out: torch.Tensor, layout: ConvLayout) -> None:
+    """out[t] = h[t] + sum_j w[:, j] h[t - taps + 1 + j] over a request's rows (ext: the normed rows in the layout of `ConvLayout`, taps =
+    halo + 1, w float32 [H, taps]); the request's state becomes the last `halo` rows of its run."""
+    T, H = out.shape
+    _check("ext", ext, torch.float32, (layout.rows(T), H))
+    _check("w", w, torch.float32, (H, layout.halo + 1))
+    _check("out", out)
+    L.call("ib_causal_conv_rows", ext.data_ptr(), w.data_ptr(), layout.halo + 1, out.data_ptr(), dtype_code(out.dtype), T, H, layout.seg_of_token.data_ptr(),
+           layout.seg_start.data_ptr(), layout.seg_slot.data_ptr(), layout.n_segments, layout.state.data_ptr(), layout.slot_stride, _stream())
+
+
+def depth_average(x: torch.Tensor, delta: Optional[torch.Tensor], delta_scale: Optional[torch.Tensor], stack: torch.Tensor, k: int, mix: torch.Tensor,
+                  delta_bias: Optional[torch.Tensor] = None) -> None:
+    """X = x + delta_scale * (sum_p delta[p] + delta_bias); stack[k] = X; x = sum_{j <= k} mix[j] * stack[j] (in place). stack float32 [n, T, H], k >= 1."""
+    T, H = x.shape
+    _check("x", x, torch.float32)
+    _check("stack", stack, torch.float32)
+    if stack.dim() != 3 or tuple(stack.shape[1:]) != (T, H) or not 1 <= k < stack.shape[0]:
+        raise L.KernelError(f"depth_average: stack must be [more than {k}, {T}, {H}], got {tuple(stack.shape)}")
+    _check("mix", mix, torch.float32, (k + 1,))
+    P = 0
+    if delta is not None:
+        _check("delta", delta, torch.float32)
+        if delta.dim() != 3 or tuple(delta.shape[1:]) != (T, H):
+            raise L.KernelError(f"delta must be [P, {T}, {H}], got {tuple(delta.shape)}")
+        P = delta.shape[0]
+    for name, v in (("delta_scale", delta_scale), ("delta_bias", delta_bias)):
+        if v is not None:
+            _check(name, v, torch.float32, (H,))
+    L.call("ib_depth_average", x.data_ptr(), _ptr(delta), P, T * H, _ptr(delta_scale), _ptr(delta_bias), stack.data_ptr(), T * H, k, mix.data_ptr(), T, H, _stream())
+
+
+def scale_values(v: torch.Tensor, s: float) -> None:
+    """v *= s, float32, in place."""
+    _check("v", v, torch.float32)
+    L.call("ib_scale_values", v.data_ptr(), v.numel(), float(s), _stream())
+
+
+# ---------------------------------------------------------------- gated linear recurrence (csrc/gated_recurrence.cu)
+L.register("ib_gated_recurrence", [L._p, L._i, L._ll, L._p, L._p, L._p, L._ll, L._p, L._p, L._i, L._p, L._i, L._i, L._i, L._p])
+L.register("ib_head_rmsnorm", [L._p, L._p, L._f, L._p, L._i, L._ll, L._i, L._p])
+
+
+def gated_recurrence(proj: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor,
+                     n_segments: int, out: torch.Tensor, heads: int, dim: int, vdim: int) -> None:
+    """proj float32 [P, T, heads * (2 dim + vdim)] = partial sums of [q | f | v]; state float32 [slots, heads, dim, vdim], advanced in place for the
+    step's segments; out float32 [T, heads, vdim] = S^T q after every token."""
+    _check("proj", proj, torch.float32)
+    P, T, R = proj.shape
+    if R != heads * (2 * dim + vdim):
+        raise L.KernelError(f"gated_recurrence: the projection has {R} columns, expected {heads * (2 * dim + vdim)}")
+    _check("f_bias", f_bias, torch.float32, (heads * dim,))
+    _check("lower", lower, torch.float32, (heads * dim,))
+    _check("state", state, torch.float32)
+    if tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise L.KernelError(f"gated_recurrence: the state must be [slots, {heads}, {dim}, {vdim}], got {tuple(state.shape)}")
+    _check("out", out, torch.float32, (T, heads, vdim))
+    _check("seg_start", seg_start, torch.int32)
+    _check("seg_slot", seg_slot, torch.int32)
+    L.call("ib_gated_recurrence", proj.data_ptr(), P, T * R, f_bias.data_ptr(), lower.data_ptr(), state.data_ptr(), heads * dim * vdim, seg_start.data_ptr(),
+           seg_slot.data_ptr(), n_segments, out.data_ptr(), heads, dim, vdim, _stream())
+
+
+def head_rmsnorm(o: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out[t, a, :] = w * o[t, a, :] / sqrt(mean(o[t, a, :]^2) + eps); o float32 [T, heads, V], out [T, heads * V] in its own dtype."""
+    T, heads, V = o.shape
+    _check("o", o, torch.float32)
+    _check("w", w, torch.float32, (V,))
+    _check("out", out, None, (T, heads * V))
+    L.call("ib_head_rmsnorm", o.data_ptr(), w.data_ptr(), float(eps), out.data_ptr(), dtype_code(out.dtype), T * heads, V, _stream())

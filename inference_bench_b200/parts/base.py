@@ -27,6 +27,8 @@ class WeightSpec:
     "matrix": kept in bfloat16 unless stored in 32-bit; random ~ N(0, std)
     "norm":   per-channel scale used in float32; random 1 + U(-0.1, 0.1)
     "norm_offset": the same stored around zero (the scale is 1 + w); random U(-0.2, 0.2)
+    "gate_floor": lower bounds of a forget gate, used in float32; random U(0, 0.9)
+    "mix":    weights of an average over the n entries of the tensor's last axis, used in float32; random around 1 / n
     "table":  integer table, int32."""
     name: str
     shape: tuple[int, ...]
@@ -58,7 +60,24 @@ class FixedState:
     dtype: torch.dtype = torch.float32
 
 
-CacheNeed = Optional[object]  # PagedKV | PagedRows | FixedState | None
+@dataclass(frozen=True)
+class Several:
+    """More than one thing for one execution (a block with state of its own beside its mixer's cache): the execution gets a tuple
+    of views in the order of `needs`, None where an item is None."""
+    needs: tuple
+
+
+CacheNeed = Optional[object]  # PagedKV | PagedRows | FixedState | Several | None
+
+
+def flat_needs(needs) -> list:
+    """Every single need (no None, no `Several`) among an execution list's needs."""
+    out = []
+    for n in needs:
+        for m in (n.needs if isinstance(n, Several) else (n,)):
+            if m is not None:
+                out.append(m)
+    return out
 
 
 class Part:
@@ -95,6 +114,8 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     adds_to_residual = False   # True: forward takes `residual=` and may add its contribution there itself
+    out_bias: Optional[torch.Tensor] = None   # float32 [H], set at bind: a vector that belongs to every row of the contribution and that the
+                                              # kernel which adds the contribution to the stream adds with it (only blocks that say so take such a mixer)
 
     def cache_need(self) -> CacheNeed:
         return None
@@ -134,8 +155,14 @@ class Block:
     def __init__(self, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Norm, feed_forward: FeedForward):
         self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward = mixer_norm, mixer, feed_forward_norm, feed_forward
 
+    takes_out_bias = False   # True: the arrangement adds a mixer's `out_bias` where it adds the mixer's contribution
+
     def parts(self) -> list[Part]:
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
+    def cache_need(self) -> CacheNeed:
+        """What an execution of this block asks of the cache manager: its mixer's need, unless the arrangement has state of its own."""
+        return self.mixer.cache_need()
 
     def forward(self, ctx: "StepContext", x: torch.Tensor, pending: Optional[torch.Tensor], cache) -> Optional[torch.Tensor]:
         """Runs the block on x (in place). `pending` is a contribution not yet added to x; the

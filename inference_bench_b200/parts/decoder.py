@@ -55,7 +55,7 @@ class Decoder:
     def cache_needs(self) -> list:
         """Per schedule entry: the need of the execution's own cache, or None when it has none or
         reads another entry's."""
-        return [None if e.cache_of is not None else self.blocks[e.layer].mixer.cache_need() for e in self.plan.schedule]
+        return [None if e.cache_of is not None else self.blocks[e.layer].cache_need() for e in self.plan.schedule]
 
     def cache_sources(self) -> list[int]:
         """Per schedule entry: the entry whose cache it uses (itself when it owns one)."""

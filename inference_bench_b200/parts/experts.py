@@ -5,6 +5,8 @@ plus (optionally) one shared expert that every token uses.
     largest s, the best `groups_keep` groups stay;  of their experts the `top` with the largest s are chosen;
     out = sum_e weight_e * down_e(silu(gate_e h) * up_e h)  [+ shared(h)],   weight_e = s_e * route_scale
     (with `renorm`: s_e / sum of the chosen s, times route_scale).
+`score="sigmoid"`: s_e = sigmoid of expert e's own logit instead of the softmax. `weight_on="input"`: the weight scales what the expert
+reads, out = sum_e down_e(silu(gate_e (weight_e h)) * up_e (weight_e h)), which is not the same thing for a gated expert.
 The step's (token, expert) pairs are regrouped by expert on the device (no trip to the host, so the step can be captured),
 the experts' products run on the regrouped rows, and the weighted sum returns them to token order.
 """
@@ -21,9 +23,13 @@ from .base import WeightSpec
 @base.register_feed_forward("routed_experts")
 class RoutedExperts(base.FeedForward):
     def __init__(self, prefix: str, hidden: int, expert_ff: int, experts: int, top: int, route_scale: float = 1.0, groups: int = 1, groups_keep: int = 1,
-                 shared_ff: int = 0, renorm: bool = False, names: tuple = ("router", "e{}", "shared", "gate", "up", "down")):
+                 shared_ff: int = 0, renorm: bool = False, names: tuple = ("router", "e{}", "shared", "gate", "up", "down"), score: str = "softmax",
+                 weight_on: str = "output"):
         if not 0 < top <= experts or experts % groups or not 0 < groups_keep <= groups:
             raise ValueError(f"top {top} of {experts} experts in {groups} groups of which {groups_keep} stay")
+        if score not in ("softmax", "sigmoid") or weight_on not in ("output", "input"):
+            raise ValueError(f"score {score!r} (softmax, sigmoid) or weight_on {weight_on!r} (output, input) is not known")
+        self.score, self.weight_on = score, weight_on
         self.prefix, self.hidden, self.expert_ff, self.experts, self.top = prefix, hidden, expert_ff, experts, top
         self.route_scale, self.groups, self.groups_keep, self.shared_ff, self.renorm, self.names = route_scale, groups, groups_keep, shared_ff, renorm, tuple(names)
         self.w_router = self.w_gu = self.w_d = self.shared_gu = self.shared_d = None
@@ -58,7 +64,8 @@ class RoutedExperts(base.FeedForward):
         R = T * top
         logits = rt.linear(h, self.w_router)                     # float32 partial sums [P, T, E]
         idx, wt = rt.empty((T, top), torch.int32), rt.empty((T, top), torch.float32)
-        ops.moe_route(logits, self.groups, self.groups_keep, top, self.route_scale, self.renorm, idx, wt)
+        ops.moe_route(logits, self.groups, self.groups_keep, top, self.route_scale, self.renorm, idx, wt, self.score)
+        on_input = self.weight_on == "input"
         offsets, tile_start = rt.empty((E + 1,), torch.int32), rt.empty((E + 1,), torch.int32)
         row_of_pair, token_of_row = rt.empty((R,), torch.int32), rt.empty((R,), torch.int32)
         how = rt.options.expert_gemm
@@ -69,7 +76,10 @@ class RoutedExperts(base.FeedForward):
             # the tcgen05 kernel of the single-matrix products, its tiles taking their expert from the tile table
             ops.moe_sort(idx, E, offsets, tile_start, row_of_pair, token_of_row, tile_rows=bn)
             xs = rt.empty((R, self.hidden))
-            ops.gather_rows(h, token_of_row, xs)
+            if on_input:
+                ops.scatter_scaled_rows(h, row_of_pair, wt, xs)
+            else:
+                ops.gather_rows(h, token_of_row, xs)
             G.gemm_grouped_swiglu(xs, self.w_gu, act, bn, offsets, tile_start, rt.status)
             G.gemm_grouped(act, self.w_d, y, bn, offsets, tile_start, rt.status)
         else:
@@ -77,9 +87,13 @@ class RoutedExperts(base.FeedForward):
                 raise ValueError(f"expert_gemm = \"tcgen05\" needs bfloat16 and inner sizes that are multiples of 8 (of 64 for few tokens), got {self.hidden} and {self.expert_ff}")
             tc = how != "simt"
             ops.moe_sort(idx, E, offsets, tile_start, row_of_pair, token_of_row)
-            ops.gemm_grouped(h, token_of_row, self.w_gu, act, offsets, tile_start, gated=True, tensor_cores=tc and ops.rows_mma_fits(h, self.w_gu))
+            src, rows = h, token_of_row
+            if on_input:   # the rows in the experts' order, each times its weight; the product then reads them as they lie
+                src, rows = rt.empty((R, self.hidden)), None
+                ops.scatter_scaled_rows(h, row_of_pair, wt, src)
+            ops.gemm_grouped(src, rows, self.w_gu, act, offsets, tile_start, gated=True, tensor_cores=tc and ops.rows_mma_fits(src, self.w_gu))
             ops.gemm_grouped(act, None, self.w_d, y, offsets, tile_start, gated=False, tensor_cores=tc and ops.rows_mma_fits(act, self.w_d))
         shared = rt.linear(rt.gate_up_act(h, self.shared_gu), self.shared_d) if self.shared_ff else None
         out = rt.empty((1, T, self.hidden), torch.float32)
-        ops.moe_combine(y, row_of_pair, wt, shared, out[0])
+        ops.moe_combine(y, row_of_pair, wt, shared, out[0], weighted=not on_input)
         return out

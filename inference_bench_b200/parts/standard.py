@@ -48,6 +48,32 @@ class RMSNorm(base.Norm):
         return out
 
 
+@base.register_norm("layernorm")
+class LayerNorm(base.Norm):
+    """y = w * (x - mean(x)) / sqrt(mean((x - mean)^2) + eps), no bias, float32 arithmetic, fused with the residual add that precedes
+    it. `forward` takes the extras a block may need from that kernel: a per-channel scale and a bias on the contribution it adds, a
+    copy of the updated stream, and a layout of the normed rows for a convolution over time (`ops.ConvLayout`; the rows then stay
+    float32 and keep their place in that layout)."""
+
+    def __init__(self, name: str, size: int, eps: float):
+        self.name, self.size, self.eps = name, size, eps
+        self.w: Optional[torch.Tensor] = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.name, (self.size,), role="norm")]
+
+    def bind(self, weights, rt):
+        self.w = rt.vector(weights[self.name])
+
+    def forward(self, ctx, x, delta, rows=None, delta_scale=None, delta_bias=None, x_copy=None, layout=None):
+        if layout is not None:
+            out = ctx.rt.empty((layout.rows(x.shape[0]), self.size), torch.float32)
+        else:
+            out = ctx.rt.empty((x.shape[0] if rows is None else rows.shape[0], self.size))
+        ops.add_layernorm(x, delta, self.w, out, self.eps, rows, delta_scale, delta_bias, x_copy, layout)
+        return out
+
+
 # ------------------------------------------------------------------------------------------ position
 @base.register_position_encoding("rope")
 class RotaryEmbedding(base.PositionEncoding):
@@ -55,9 +81,17 @@ class RotaryEmbedding(base.PositionEncoding):
     inv_freq_i = theta^(-2i/rotary_dim), angle = float(pos) * inv_freq_i in float32
     (crates/kir/tests/golden/attention/RopeKvWrite_bf16x2_sm120.cu:32-35, 200-206)."""
 
-    def __init__(self, rotary_dim: int, theta: float, pairing: str = "half"):
+    def __init__(self, rotary_dim: int, theta: float, pairing: str = "half", scaling: Optional[tuple] = None):
         """pairing: which entries a mixer turns together with these angles: "half" pairs entry i with i + rotary_dim/2,
-        "interleaved" pairs entry 2i with 2i + 1. The tables are the same; the mixer's kernel does the pairing."""
+        "interleaved" pairs entry 2i with 2i + 1. The tables are the same; the mixer's kernel does the pairing.
+        scaling: None or (factor, low, high, original): frequencies are rescaled by wavelength l = 2 pi / f in three bands. Where
+        l < original / high the frequency stays; where l > original / low it becomes f / factor; between the two it is
+        (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+        if scaling is not None:
+            scaling = tuple(float(v) for v in scaling)
+            if len(scaling) != 4 or scaling[0] <= 0 or scaling[2] == scaling[1] or scaling[3] <= 0:
+                raise ValueError(f"rotary scaling must be (factor, low, high, original) with high != low, got {scaling}")
+        self.scaling = scaling
         if rotary_dim % 2:
             raise ValueError(f"rotary_dim {rotary_dim} must be even")
         if pairing not in ("half", "interleaved"):
@@ -67,10 +101,17 @@ class RotaryEmbedding(base.PositionEncoding):
 
     def bind(self, weights, rt):
         i = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
-        self.inv_freq = rt.upload((1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64), i / self.rotary_dim)).to(torch.float32))
+        f = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64), i / self.rotary_dim)
+        if self.scaling is not None:
+            factor, low, high, original = self.scaling
+            wavelength = 2.0 * math.pi / f
+            blend = (original / wavelength - low) / (high - low)
+            mid = (1.0 - blend) * f / factor + blend * f
+            f = torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, mid))
+        self.inv_freq = rt.upload(f.to(torch.float32))
 
     def tables(self, ctx):
-        key = ("rope", self.rotary_dim, self.theta)
+        key = ("rope", self.rotary_dim, self.theta, self.scaling)
         if key not in ctx.memo:
             half = self.rotary_dim // 2
             cos = ctx.rt.empty((ctx.n_tokens, half), torch.float32)
@@ -99,53 +140,102 @@ class Attention(base.Mixer):
     per-head norm then RoPE (crates/kir/src/cuda/attention/common.rs:49-96);
     s = q.k / sqrt(head_dim), keys visible when key <= pos and, with a window W, key > pos - W
     (crates/kir/src/cuda/attention/flash_mma.rs:193); out = Wo (softmax(s) v).
-    With own_kv=False the layer has only a q projection and reads the cache it is given."""
+    With own_kv=False the layer has only a q projection and reads the cache it is given.
+
+    Variants, each a constructor parameter: `bias` (q, k, v and the output projection have bias vectors; the output's is handed
+    to the block as `out_bias`), `softcap` c (s <- c tanh(s / c) after the scale), `sink` (the softmax's denominator has one added:
+    a key of score 0 that has no value), `v_head_dim` (values of another size than queries and keys), `names` (what the q, k, v,
+    o matrices, the two norms and a bias are called under `prefix`)."""
+
+    NAMES = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "q_norm.weight", "k_norm.weight", "{}.bias")
 
     def __init__(self, prefix: str, hidden: int, heads: int, kv_heads: int, head_dim: int, qk_norm: bool, norm_eps: float,
-                 position: base.PositionEncoding, window: Optional[int] = None, own_kv: bool = True, scale: Optional[float] = None):
+                 position: base.PositionEncoding, window: Optional[int] = None, own_kv: bool = True, scale: Optional[float] = None,
+                 bias: bool = False, softcap: Optional[float] = None, sink: bool = False, v_head_dim: Optional[int] = None, names: tuple = NAMES):
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
         if getattr(position, "pairing", "half") != "half":
             raise ValueError("this attention turns entry i with i + rotary_dim/2: it needs a position encoding with pairing=\"half\"")
+        if softcap is not None and not softcap > 0:
+            raise ValueError(f"softcap must be positive, got {softcap}")
+        if bias and not own_kv:
+            raise ValueError("an attention that reads another layer's cache has no biased k and v projections")
         self.prefix, self.hidden, self.heads, self.kv_heads, self.head_dim = prefix, hidden, heads, kv_heads, head_dim
+        self.v_head_dim = v_head_dim or head_dim
         self.qk_norm, self.norm_eps, self.position, self.window, self.own_kv = qk_norm, norm_eps, position, window, own_kv
         self.scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)  # crates/specrt/src/codegen.rs:147
-        self.wqkv = self.wo = self.q_norm = self.k_norm = None
+        self.bias, self.softcap, self.sink, self.names = bool(bias), softcap, bool(sink), tuple(names)
+        self.wqkv = self.wo = self.q_norm = self.k_norm = self.qkv_bias = None
+
+    @property
+    def plain(self) -> bool:
+        """The form every attention kernel of the engine computes: one head size, no bias, plain scores, plain softmax."""
+        return not (self.bias or self.softcap or self.sink) and self.v_head_dim == self.head_dim
 
     def cache_need(self):
-        return PagedKV(self.kv_heads, self.head_dim, self.window) if self.own_kv else None
+        # one row size for keys and values: the larger of the two (the kernels are told both)
+        return PagedKV(self.kv_heads, max(self.head_dim, self.v_head_dim), self.window) if self.own_kv else None
+
+    def _n(self, i: int) -> str:
+        return f"{self.prefix}.{self.names[i]}"
+
+    def _b(self, i: int) -> str:
+        """The bias of matrix i: its name without a trailing ".weight", in the bias pattern."""
+        stem = self.names[i][:-len(".weight")] if self.names[i].endswith(".weight") else self.names[i]
+        return f"{self.prefix}.{self.names[6].format(stem)}"
 
     def weight_specs(self):
-        p, hd = self.prefix, self.head_dim
-        specs = [WeightSpec(f"{p}.q_proj.weight", (self.heads * hd, self.hidden)), WeightSpec(f"{p}.o_proj.weight", (self.hidden, self.heads * hd))]
+        hd, vd = self.head_dim, self.v_head_dim
+        sizes = [self.heads * hd, self.kv_heads * hd, self.kv_heads * vd]
+        specs = [WeightSpec(self._n(0), (sizes[0], self.hidden)), WeightSpec(self._n(3), (self.hidden, self.heads * vd))]
         if self.own_kv:
-            specs += [WeightSpec(f"{p}.k_proj.weight", (self.kv_heads * hd, self.hidden)), WeightSpec(f"{p}.v_proj.weight", (self.kv_heads * hd, self.hidden))]
+            specs += [WeightSpec(self._n(1), (sizes[1], self.hidden)), WeightSpec(self._n(2), (sizes[2], self.hidden))]
         if self.qk_norm:
-            specs.append(WeightSpec(f"{p}.q_norm.weight", (hd,), role="norm"))
+            specs.append(WeightSpec(self._n(4), (hd,), role="norm"))
             if self.own_kv:
-                specs.append(WeightSpec(f"{p}.k_norm.weight", (hd,), role="norm"))
+                specs.append(WeightSpec(self._n(5), (hd,), role="norm"))
+        if self.bias:
+            specs += [WeightSpec(self._b(i), (sizes[i],), std=0.1) for i in range(3)] + [WeightSpec(self._b(3), (self.hidden,), std=0.1)]
         return specs
 
     def bind(self, weights, rt):
-        p = self.prefix
-        rows = [weights[f"{p}.q_proj.weight"]]
+        rows = [weights[self._n(0)]]
         if self.own_kv:
-            rows += [weights[f"{p}.k_proj.weight"], weights[f"{p}.v_proj.weight"]]
+            rows += [weights[self._n(1)], weights[self._n(2)]]
         else:  # keep the [q | k | v] row layout the kernels read; the k and v rows are never used
-            z = torch.zeros((2 * self.kv_heads * self.head_dim, self.hidden), dtype=rows[0].dtype, device=rows[0].device)
+            z = torch.zeros((self.kv_heads * (self.head_dim + self.v_head_dim), self.hidden), dtype=rows[0].dtype, device=rows[0].device)
             rows.append(z)
         self.wqkv = rt.matrix(torch.cat(rows, dim=0))
-        self.wo = rt.matrix(weights[f"{p}.o_proj.weight"])
+        self.wo = rt.matrix(weights[self._n(3)])
         if self.qk_norm:
-            self.q_norm = rt.vector(weights[f"{p}.q_norm.weight"])
+            self.q_norm = rt.vector(weights[self._n(4)])
             if self.own_kv:
-                self.k_norm = rt.vector(weights[f"{p}.k_norm.weight"])
+                self.k_norm = rt.vector(weights[self._n(5)])
+        if self.bias:
+            self.qkv_bias = rt.vector(torch.cat([weights[self._b(i)].to(torch.float32) for i in range(3)]))
+            self.out_bias = rt.vector(weights[self._b(3)])
         self.position.bind(weights, rt)
 
     adds_to_residual = True   # the output projection may add to the residual stream in its epilogue
 
+    def _forward_variant(self, ctx, h, cache):
+        """Any of the variants: the projection's partial sums go through the q/k kernel that adds biases and takes two head sizes, then
+        the attention kernels that cap scores and count the sink."""
+        rt = ctx.rt
+        from ..kernels import attention
+        cos, sin = self.position.tables(ctx)
+        qkv = rt.linear(h, self.wqkv)
+        q = rt.empty((ctx.n_tokens, self.heads * self.head_dim))
+        ops.qk_norm_rope_kv(qkv, self.q_norm, self.k_norm, self.norm_eps, cos, sin, ctx.positions, ctx.seg_of_token, q, cache, self.heads,
+                            rt.status, write_kv=self.own_kv, bias=self.qkv_bias, qk_dim=self.head_dim, v_dim=self.v_head_dim)
+        out = attention.paged_attention(ctx, q, cache, self.heads, self.window, self.scale, qk_dim=self.head_dim, v_dim=self.v_head_dim,
+                                        softcap=self.softcap or 0.0, sink=self.sink)
+        return rt.linear(out, self.wo)
+
     def forward(self, ctx, h, cache, residual=None):
         rt = ctx.rt
+        if not self.plain:
+            return self._forward_variant(ctx, h, cache)
         cos, sin = self.position.tables(ctx)
         from ..kernels import attention
         q = attention.project_qkv(ctx, h, self.wqkv, self.q_norm, self.k_norm, self.norm_eps, cos, sin, cache, self.heads, self.own_kv)
@@ -218,8 +308,9 @@ class LinearHead(base.Head):
     its own (a tied model ignores lm_head.weight even when the file has it:
     crates/specrt/src/weights.rs:1396-1405)."""
 
-    def __init__(self, name: str, vocab: int, hidden: int, tied_to: Optional[str] = None):
-        self.name, self.vocab, self.hidden, self.tied_to = name, vocab, hidden, tied_to
+    def __init__(self, name: str, vocab: int, hidden: int, tied_to: Optional[str] = None, scale: float = 1.0):
+        """scale: a constant on the logits."""
+        self.name, self.vocab, self.hidden, self.tied_to, self.scale = name, vocab, hidden, tied_to, float(scale)
         self.w = None
 
     def weight_specs(self):
@@ -232,6 +323,8 @@ class LinearHead(base.Head):
         out = ctx.rt.linear(h, self.w, allow_split=False)
         if out.shape[0] != 1:
             raise RuntimeError(f"the head's product came back in {out.shape[0]} partial sums although it asked for one")
+        if self.scale != 1.0:
+            ops.scale_values(out[0], self.scale)
         return out[0]
 
 
@@ -241,6 +334,11 @@ class PreNormBlock(base.Block):
     """x += mixer(norm(x)); x += feed_forward(norm(x)) (crates/specrt/graphs/decoder.toml:168-303).
     Each residual add is fused into the norm that follows it, so the feed-forward's contribution
     is handed to the next block (or the final norm) instead of being added here."""
+
+    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward):
+        super().__init__(mixer_norm, mixer, feed_forward_norm, feed_forward)
+        if getattr(mixer, "bias", False):
+            raise ValueError("this arrangement does not add a mixer's output bias")
 
     def forward(self, ctx, x, pending, cache):
         h = self.mixer_norm.forward(ctx, x, pending)
@@ -258,6 +356,8 @@ class OutNormBlock(base.Block):
 
     def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward, residual_mult: float = 1.0):
         super().__init__(mixer_norm, mixer, feed_forward_norm, feed_forward)
+        if getattr(mixer, "bias", False):
+            raise ValueError("this arrangement does not add a mixer's output bias")
         self.residual_mult = residual_mult
 
     def forward(self, ctx, x, pending, cache):

@@ -30,7 +30,7 @@ import sys
 from pathlib import Path
 
 PAGE_SIZE = 16
-MAX_LIVE = 8
+MAX_LIVE = 4
 
 
 def build_runner(model, dtype: str, max_tokens: int, page_size: int = PAGE_SIZE, max_requests: int = MAX_LIVE, device: str = "cuda:0", options=None):

@@ -31,6 +31,10 @@ def random_tensor(spec: WeightSpec, seed: int, device="cpu", dtype=torch.bfloat1
         t = 1.0 + (torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32) * 0.2 - 0.1)
     elif spec.role == "norm_offset":
         t = torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32) * 0.4 - 0.2
+    elif spec.role == "gate_floor":    # lower bounds of a forget gate, in (0, 1)
+        t = torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32) * 0.9
+    elif spec.role == "mix":           # weights of an average over n inputs: around 1 / n each
+        t = (0.7 + 0.6 * torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32)) / max(1, spec.shape[-1])
     elif spec.role == "matrix":
         t = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32) * (spec.std if std is None else std)
     else:
