@@ -85,27 +85,37 @@ def rotate(x, positions, freqs):
 
 
 # ------------------------------------------------------------------------------------------ mixers
-def attention(h, m, w, p, pos0=0):
-    """Windowed grouped-query attention with biases, capped scores and a softmax whose denominator has one added."""
+def attention_core(q, k, v, scale, cap=None, window=None, sink=True):
+    """q [T, H, D], k [T, G, D], v [T, G, V] of one sequence (rows are positions 0..T-1) -> [T, H, V]. Query head a reads key/value head
+    a // (H / G); position i sees j with 0 <= i - j < window; scores are capped by cap * tanh(s / cap); with `sink` the softmax's
+    denominator is 1 + sum exp(s)."""
+    T, H, _ = q.shape
+    G, V = k.shape[1], v.shape[2]
+    out = torch.zeros((T, H, V), dtype=F64)
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    seen = (i - j >= 0) if window is None else (i - j >= 0) & (i - j < window)
+    for a in range(H):
+        g = a // (H // G)
+        s = (d(q[:, a]) @ d(k[:, g]).T) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        e = torch.where(seen, torch.exp(s), torch.zeros_like(s))
+        out[:, a] = (e / ((1.0 if sink else 0.0) + e.sum(-1, keepdim=True))) @ d(v[:, g])
+    return out
+
+
+def attention(h, m, w, p):
+    """Windowed grouped-query attention with biases, partly turned heads, capped scores and the softmax with one added."""
     T = h.shape[0]
     H, G, D, V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     q = (h @ d(w[p + ".q"]).T + d(w[p + ".q.b"])).view(T, H, D)
     k = (h @ d(w[p + ".k"]).T + d(w[p + ".k.b"])).view(T, G, D)
     v = (h @ d(w[p + ".v"]).T + d(w[p + ".v.b"])).view(T, G, V)
-    pos = torch.arange(pos0, pos0 + T)
+    pos = torch.arange(T)
     fr = rotary_frequencies(m["rot"])
     q, k = rotate(q, pos, fr), rotate(k, pos, fr)
-    cap, scale, win = float(m["softcap"]), float(m["scale"]), int(m["mask"]["size"])
-    out = torch.zeros((T, H, V), dtype=F64)
-    per = H // G
-    for a in range(H):
-        g = a // per
-        s = (q[:, a] @ k[:, g].T) * scale
-        s = cap * torch.tanh(s / cap)
-        i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
-        seen = (i - j >= 0) & (i - j < win)
-        e = torch.where(seen, torch.exp(s), torch.zeros_like(s))
-        out[:, a] = (e / (1.0 + e.sum(-1, keepdim=True))) @ v[:, g]
+    win = (m.get("mask") or {}).get("size")
+    out = attention_core(q, k, v, float(m["scale"]), m.get("softcap"), None if win is None else int(win))
     return out.reshape(T, H * V) @ d(w[p + ".o"]).T + d(w[p + ".o.b"])
 
 
@@ -117,13 +127,21 @@ def hgrn2(h, m, w, p, eps, state=None):
     low = d(w[p + ".lower"]).view(H, D)
     f = low + (1.0 - low) * torch.sigmoid(h @ d(w[p + ".f"]).T + d(w[p + ".f.b"])).view(T, H, D)
     v = (h @ d(w[p + ".v"]).T).view(T, H, V)
-    S = torch.zeros((H, D, V), dtype=F64) if state is None else state.clone()
-    o = torch.zeros((T, H, V), dtype=F64)
-    for t in range(T):
-        S = f[t][:, :, None] * S + (1.0 - f[t])[:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    o, S = recurrence_core(q, f, v, state)
     o = rms_unit(o, eps) * d(w[p + ".norm"])
     return o.reshape(T, H * V) @ d(w[p + ".o"]).T, S
+
+
+def recurrence_core(q, f, v, state=None):
+    """q, f [T, H, D], v [T, H, V]: S <- diag(f_t) S + (1 - f_t) v_t^T, o_t = S^T q_t per head; returns (o [T, H, V], the last S [H, D, V])."""
+    T, H, D = q.shape
+    V = v.shape[2]
+    S = torch.zeros((H, D, V), dtype=F64) if state is None else d(state).clone()
+    o = torch.zeros((T, H, V), dtype=F64)
+    for t in range(T):
+        S = d(f[t])[:, :, None] * S + (1.0 - d(f[t]))[:, :, None] * d(v[t])[:, None, :]
+        o[t] = torch.einsum("hdv,hd->hv", S, d(q[t]))
+    return o, S
 
 
 # ------------------------------------------------------------------------------------------ feed-forward
@@ -177,3 +195,30 @@ def hidden_states(cfg, w, tokens):
 def logits(cfg, w, tokens):
     x = hidden_states(cfg, w, tokens)[-1]
     return layer_norm(x, w["final.norm"], float(cfg["norm"]["eps"])) @ d(w["head"]).T * float(cfg.get("logit_scale", 1.0))
+
+
+class PlainBusadra:
+    """The plain model of a folder with config.json and model.safetensors."""
+
+    def __init__(self, model_dir):
+        import json
+        from pathlib import Path
+
+        from inference_bench_b200.weights.safetensors_io import Checkpoint
+        self.cfg = json.loads((Path(model_dir) / "config.json").read_text())
+        ck = Checkpoint(model_dir)
+        self.w = {n: ck.read(n) for n in ck.names()}
+        ck.close()
+
+    def hidden_states(self, tokens):
+        return hidden_states(self.cfg, self.w, tokens)
+
+    def logits(self, tokens):
+        return logits(self.cfg, self.w, tokens)
+
+    def greedy(self, prompt, n):
+        toks, out = list(prompt), []
+        for _ in range(n):
+            out.append(int(self.logits(toks)[-1].argmax()))
+            toks.append(out[-1])
+        return out
