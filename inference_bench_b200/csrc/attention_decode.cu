@@ -45,7 +45,8 @@ __global__ void __launch_bounds__(kWarps * 32)
     decode_split_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ dec_tokens,
                         const int* __restrict__ positions, const int* __restrict__ seg_of_token, int window, float scale_log2e,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int heads, int max_slices, int tiles_per_slice,
-                        unsigned* __restrict__ status) {
+                        unsigned* __restrict__ status, float cap_pre) {
+  // cap_pre != 0: a raw product s counts as tanh(s * cap_pre) (the caller's scale_log2e is then cap * log2 e)
   constexpr int CPR = HD / 8;              // 16-byte chunks per row
   constexpr int TILE = kTile * HD * 2;     // bytes of one K (or V) tile
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -172,7 +173,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 #pragma unroll
       for (int e = 0; e < 4; e++) {
         int key = tile * kTile + wkey + 8 * j + 2 * tq + (e & 1);
-        float v = (key >= k_begin && key < k_end) ? s[j][e] * scale_log2e : -INFINITY;
+        float v = (key >= k_begin && key < k_end) ? (cap_pre != 0.f ? ib::tanh_fast(s[j][e] * cap_pre) : s[j][e]) * scale_log2e : -INFINITY;
         s[j][e] = v;
         mn[e >> 1] = fmaxf(mn[e >> 1], v);
       }
@@ -269,7 +270,8 @@ template <int HD>
 __global__ void __launch_bounds__(kCombineThreads)
     decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ dec_tokens,
                           const int* __restrict__ positions, int window, __nv_bfloat16* __restrict__ out, int heads, int max_slices,
-                          int tiles_per_slice, unsigned* __restrict__ status) {
+                          int tiles_per_slice, unsigned* __restrict__ status, int sink) {
+  // sink: one more term of score 0 and no value in the denominator
   constexpr int DQ = HD / 4;
   constexpr int SG = kCombineThreads / DQ;
   __shared__ float4 o_red[SG][DQ];
@@ -338,6 +340,7 @@ __global__ void __launch_bounds__(kCombineThreads)
       O.z += v.z;
       O.w += v.w;
     }
+    if (sink && M > -INFINITY) Lsum += exp2f(-M);
     if (!(Lsum > 0.f)) {
       O = make_float4(0.f, 0.f, 0.f, 0.f);
       Lsum = 1.f;
@@ -383,7 +386,8 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
     decode_stream_kernel(const __nv_bfloat16* __restrict__ q, RawQkv raw, IbKvView kv, const int* __restrict__ dec_tokens, const int* __restrict__ positions,
                          const int* __restrict__ seg_of_token, int window, float scale_log2e, float* __restrict__ part_o,
                          float* __restrict__ part_ml, int heads, int n_dec, int max_slices, int tiles_per_slice, int merge_cols,
-                         const __grid_constant__ CUtensorMap kv_map, long long view_row0, unsigned long long wait_ns, unsigned* __restrict__ status) {
+                         const __grid_constant__ CUtensorMap kv_map, long long view_row0, unsigned long long wait_ns, unsigned* __restrict__ status,
+                         float cap_pre) {
   constexpr int CPR = HD / 8;
   constexpr int TILE = kTile * HD * 2;
   constexpr int HB = HD / 64;
@@ -731,7 +735,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
 #pragma unroll
         for (int e = 0; e < 4; e++) {
           const int key = tile * kTile + wkey + 8 * j + 2 * tq + (e & 1);
-          const float v = (key >= k_begin && key < k_end) ? s[j][e] * scale_log2e : -INFINITY;
+          const float v = (key >= k_begin && key < k_end) ? (cap_pre != 0.f ? ib::tanh_fast(s[j][e] * cap_pre) : s[j][e]) * scale_log2e : -INFINITY;
           s[j][e] = v;
           mn[e >> 1] = fmaxf(mn[e >> 1], v);
         }
@@ -840,7 +844,8 @@ inline int stream_merge_cols(int group, int hd) {
 template <int HD, bool FUSED>
 int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token,
                   int window, float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice,
-                  const CUtensorMap* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
+                  const CUtensorMap* kv_map, long long view_row0, unsigned* status, cudaStream_t stream, float softcap = 0.f, int sink = 0) {
+  const float scale_log2e = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, cap_pre = softcap > 0.f ? scale / softcap : 0.f;
   const int group = heads / kv->kv_heads;
   const int merge_cols = stream_merge_cols(group, HD);
   const int smem = kRing * 2 * kTile * HD * 2 + 16 * HD * 2 + kWarps * 16 * 2 * 4 + kWarps * group * merge_cols * 4 + 2 * kRing * 8 + 16 + kMeta * 12 +
@@ -861,11 +866,11 @@ int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const in
   const int grid = (int)(units < (long long)sms * per_sm ? units : (long long)sms * per_sm);
   const RawQkv none = {};
   ib::launch(decode_stream_kernel<HD, FUSED>, grid, (kWarps + 1) * 32, smem, stream, (const __nv_bfloat16*)q, raw ? *raw : none, *kv, dec_tokens,
-             positions, seg_of_token, window, scale * 1.4426950408889634f, part_o, part_ml, heads, n_dec, max_slices, tiles_per_slice, merge_cols,
-             *kv_map, view_row0, ib_wait_limit_ns(), status);
+             positions, seg_of_token, window, scale_log2e, part_o, part_ml, heads, n_dec, max_slices, tiles_per_slice, merge_cols,
+             *kv_map, view_row0, ib_wait_limit_ns(), status, cap_pre);
   IB_CHECK_LAUNCH("attention_decode_stream split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
-             max_slices, tiles_per_slice, status);
+             max_slices, tiles_per_slice, status, sink);
   IB_CHECK_LAUNCH("attention_decode_stream combine");
   return 0;
 }
@@ -873,7 +878,8 @@ int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const in
 template <int HD>
 int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token, int window,
            float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice, unsigned* status,
-           cudaStream_t stream) {
+           cudaStream_t stream, float softcap = 0.f, int sink = 0) {
+  const float scale_log2e = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, cap_pre = softcap > 0.f ? scale / softcap : 0.f;
   constexpr int smem = 16 * HD * 2 + 4 * kTile * HD * 2 + 2 * kTile * 8;   // Q, two stages of K and V, key offsets
   static_assert(kWarps * 16 * HD * 4 <= 4 * kTile * HD * 2, "the merge buffer must fit in the tiles");
   static bool configured = false;
@@ -884,10 +890,10 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
   }
   dim3 grid(kv->kv_heads, n_dec, max_slices);
   ib::launch(decode_split_kernel<HD>, grid, kWarps * 32, smem, stream, (const __nv_bfloat16*)q, *kv, dec_tokens, positions, seg_of_token, window,
-             scale * 1.4426950408889634f, part_o, part_ml, heads, max_slices, tiles_per_slice, status);
+             scale_log2e, part_o, part_ml, heads, max_slices, tiles_per_slice, status, cap_pre);
   IB_CHECK_LAUNCH("attention_decode split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
-             max_slices, tiles_per_slice, status);
+             max_slices, tiles_per_slice, status, sink);
   IB_CHECK_LAUNCH("attention_decode combine");
   return 0;
 }
@@ -923,9 +929,10 @@ extern "C" int ib_make_kv_map(void* map_out, const void* pool_base, long long to
   return 0;
 }
 
-extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
-                                   const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out, int heads,
-                                   int max_slices, int tiles_per_slice, unsigned* status, cudaStream_t stream) {
+// softcap > 0: scores become softcap * tanh(score / softcap) after the scale; sink: the softmax's denominator has one added.
+extern "C" int ib_attention_decode_capped(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
+                                          const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out, int heads,
+                                          int max_slices, int tiles_per_slice, float softcap, int sink, unsigned* status, cudaStream_t stream) {
   if (n_dec == 0) return 0;
   IB_CHECK_ARG(kv && kv->base && kv->block_table, "attention_decode: the cache view has a null pointer");
   IB_CHECK_ARG(tiles_per_slice >= 1 && tiles_per_slice <= 1024, "attention_decode: %d tiles per slice", tiles_per_slice);
@@ -935,17 +942,24 @@ extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int*
   IB_CHECK_ARG(n_dec > 0 && n_dec <= 65535 && max_slices > 0 && max_slices <= 65535, "attention_decode: bad sizes n=%d slices=%d", n_dec, max_slices);
   if (kv->head_dim == 128)
     return launch<128>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
-                       status, stream);
+                       status, stream, softcap, sink);
   if (kv->head_dim == 64)
     return launch<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
-                      status, stream);
+                      status, stream, softcap, sink);
   return ib_set_error("attention_decode: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
+}
+
+extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
+                                   const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out, int heads,
+                                   int max_slices, int tiles_per_slice, unsigned* status, cudaStream_t stream) {
+  return ib_attention_decode_capped(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice, 0.f, 0,
+                                    status, stream);
 }
 
 namespace {
 int stream_entry(const void* q, const RawQkv* raw, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token,
                  int window, float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice,
-                 const void* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
+                 const void* kv_map, long long view_row0, unsigned* status, cudaStream_t stream, float softcap = 0.f, int sink = 0) {
   if (n_dec == 0) return 0;
   IB_CHECK_ARG(kv && kv->base && kv->block_table && kv_map, "attention_decode_stream: the cache view or the tensor map is a null pointer");
   IB_CHECK_ARG(kv->page_size % 8 == 0 && (kTile % kv->page_size == 0 || kv->page_size % kTile == 0),
@@ -959,15 +973,15 @@ int stream_entry(const void* q, const RawQkv* raw, const IbKvView* kv, const int
   const CUtensorMap* map = (const CUtensorMap*)kv_map;
   if (kv->head_dim == 128) {
     if (raw) return launch_stream<128, true>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                                             tiles_per_slice, map, view_row0, status, stream);
+                                             tiles_per_slice, map, view_row0, status, stream, softcap, sink);
     return launch_stream<128, false>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                                     tiles_per_slice, map, view_row0, status, stream);
+                                     tiles_per_slice, map, view_row0, status, stream, softcap, sink);
   }
   if (kv->head_dim == 64) {
     if (raw) return launch_stream<64, true>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                                            tiles_per_slice, map, view_row0, status, stream);
+                                            tiles_per_slice, map, view_row0, status, stream, softcap, sink);
     return launch_stream<64, false>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                                    tiles_per_slice, map, view_row0, status, stream);
+                                    tiles_per_slice, map, view_row0, status, stream, softcap, sink);
   }
   return ib_set_error("attention_decode_stream: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
 }
@@ -983,6 +997,16 @@ extern "C" int ib_attention_decode_stream(const void* q, const IbKvView* kv, con
   IB_CHECK_ARG(q || n_dec == 0, "attention_decode_stream: q is a null pointer");
   return stream_entry(q, nullptr, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
                       tiles_per_slice, kv_map, view_row0, status, stream);
+}
+
+// The same with capped scores (softcap > 0: softcap * tanh(score / softcap)) and, with sink, one added to the softmax's denominator.
+extern "C" int ib_attention_decode_stream_capped(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
+                                                 const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out,
+                                                 int heads, int max_slices, int tiles_per_slice, const void* kv_map, long long view_row0,
+                                                 float softcap, int sink, unsigned* status, cudaStream_t stream) {
+  IB_CHECK_ARG(q || n_dec == 0, "attention_decode_stream: q is a null pointer");
+  return stream_entry(q, nullptr, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
+                      tiles_per_slice, kv_map, view_row0, status, stream, softcap, sink);
 }
 
 // The same from the output of the q/k/v projection (float32 partial sums qkv [P][T][(heads + 2 kv_heads) * head_dim],

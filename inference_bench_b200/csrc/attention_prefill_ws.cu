@@ -86,7 +86,9 @@ __global__ void __launch_bounds__(kThreads, 2)
     prefill_ws_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                       const int* __restrict__ seg_start, const int* __restrict__ seg_pos0, int window, float scale_log2e,
                       __nv_bfloat16* __restrict__ out, int heads, const __grid_constant__ CUtensorMap kv_map, long long view_row0,
-                      unsigned long long wait_ns, unsigned* __restrict__ status) {
+                      unsigned long long wait_ns, unsigned* __restrict__ status, float cap_pre, int sink) {
+  // cap_pre != 0: a raw product s counts as tanh(s * cap_pre) (scale_log2e is then cap * log2 e); sink: the softmax has one more term
+  // of score 0 that carries no value
   using SM = Smem<HD>;
   constexpr int CPR = HD / 8, HB = HD / 64;
   constexpr int kTmemCols = 256;            // S0 [0,64) | S1 [64,128) | O [128, 128+HD); P_j lies over the first 32 columns of S_j
@@ -273,6 +275,10 @@ __global__ void __launch_bounds__(kThreads, 2)
       sm100::tmem_ld_32x32b_x32(t_lane + (j & 1) * BN, sr);
       sm100::tmem_ld_32x32b_x32(t_lane + (j & 1) * BN + 32, sr + 32);
       sm100::tmem_ld_wait();
+      if (cap_pre != 0.f) {
+#pragma unroll
+        for (int c = 0; c < BN; c++) sr[c] = __float_as_uint(ib::tanh_fast(__uint_as_float(sr[c]) * cap_pre));
+      }
       const int key0 = kt * BN;
       const bool need_mask = key0 + BN - 1 > pos_first || key0 < key_lo || (window > 0 && key0 <= pos_last - window);
       if (need_mask) {
@@ -345,6 +351,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     wait(&v_empty[(n_kt - 1) % VS], ((n_kt - 1) / VS) & 1);
     sm100::tc_fence_after();
     if (!*gave_up) {
+      if (sink) l += ex2(-m_ref);   // the sink's weight in the units of the running sum (a row that saw no key: infinite, the output is zero)
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* dst = out + ((size_t)(t0 + row) * heads + h) * HD;
 #pragma unroll 1
@@ -377,7 +384,9 @@ __global__ void __launch_bounds__(kThreads, 2)
 
 template <int HD>
 int launch(const void* q, const IbKvView* kv, const int* tile_seg, const int* tile_row0, int n_tiles, const int* seg_start, const int* seg_pos0,
-           int window, float scale, void* out, int heads, const CUtensorMap* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
+           int window, float scale, void* out, int heads, const CUtensorMap* kv_map, long long view_row0, unsigned* status, cudaStream_t stream,
+           float softcap, int sink) {
+  const float scale_log2e = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, cap_pre = softcap > 0.f ? scale / softcap : 0.f;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_ws_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<HD>::kBytes);
@@ -385,7 +394,7 @@ int launch(const void* q, const IbKvView* kv, const int* tile_seg, const int* ti
     configured = true;
   }
   ib::launch(prefill_ws_kernel<HD>, dim3(heads, n_tiles), kThreads, Smem<HD>::kBytes, stream, (const __nv_bfloat16*)q, *kv, tile_seg, tile_row0,
-             seg_start, seg_pos0, window, scale * 1.4426950408889634f, (__nv_bfloat16*)out, heads, *kv_map, view_row0, ib_wait_limit_ns(), status);
+             seg_start, seg_pos0, window, scale_log2e, (__nv_bfloat16*)out, heads, *kv_map, view_row0, ib_wait_limit_ns(), status, cap_pre, sink);
   IB_CHECK_LAUNCH("attention_prefill_ws");
   return 0;
 }
@@ -395,9 +404,10 @@ int launch(const void* q, const IbKvView* kv, const int* tile_seg, const int* ti
 // Attention for query tiles of 128 rows: tile i covers rows tile_row0[i].. of segment tile_seg[i]; list the
 // tiles that see the most keys first. kv_map: the tensor map of the view's pool (ib_make_kv_map), view_row0
 // the pool row where this view's keys of page 0, head 0 start.
-extern "C" int ib_attention_prefill_ws(const void* q, const IbKvView* kv, const int* tile_seg, const int* tile_row0, int n_tiles,
-                                       const int* seg_start, const int* seg_pos0, int window, float scale, void* out, int heads,
-                                       const void* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
+// softcap > 0: scores become softcap * tanh(score / softcap) after the scale; sink: the softmax's denominator has one added.
+extern "C" int ib_attention_prefill_ws_capped(const void* q, const IbKvView* kv, const int* tile_seg, const int* tile_row0, int n_tiles,
+                                              const int* seg_start, const int* seg_pos0, int window, float scale, void* out, int heads,
+                                              const void* kv_map, long long view_row0, float softcap, int sink, unsigned* status, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   IB_CHECK_ARG(kv && kv->base && kv->block_table && kv_map, "attention_prefill_ws: the cache view or the tensor map is a null pointer");
   IB_CHECK_ARG(kv->dtype == IB_BF16, "attention_prefill_ws: the cache must be bfloat16");
@@ -409,9 +419,16 @@ extern "C" int ib_attention_prefill_ws(const void* q, const IbKvView* kv, const 
   IB_CHECK_ARG(kv->page_stride % kv->head_dim == 0 && kv->v_offset % kv->head_dim == 0, "attention_prefill_ws: strides are not whole rows");
   if (kv->head_dim == 128)
     return launch<128>(q, kv, tile_seg, tile_row0, n_tiles, seg_start, seg_pos0, window, scale, out, heads, (const CUtensorMap*)kv_map, view_row0,
-                       status, stream);
+                       status, stream, softcap, sink);
   if (kv->head_dim == 64)
     return launch<64>(q, kv, tile_seg, tile_row0, n_tiles, seg_start, seg_pos0, window, scale, out, heads, (const CUtensorMap*)kv_map, view_row0,
-                      status, stream);
+                      status, stream, softcap, sink);
   return ib_set_error("attention_prefill_ws: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
+}
+
+extern "C" int ib_attention_prefill_ws(const void* q, const IbKvView* kv, const int* tile_seg, const int* tile_row0, int n_tiles,
+                                       const int* seg_start, const int* seg_pos0, int window, float scale, void* out, int heads,
+                                       const void* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
+  return ib_attention_prefill_ws_capped(q, kv, tile_seg, tile_row0, n_tiles, seg_start, seg_pos0, window, scale, out, heads, kv_map, view_row0, 0.f, 0, status,
+                                        stream);
 }

@@ -77,6 +77,13 @@ __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1): two special-function operations, absolute error of a few 1e-7 (the limits are exact).
+__device__ __forceinline__ float tanh_fast(float x) {
+  float t;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(x * 2.8853900817779268f));
+  return 1.f - __fdividef(2.f, t + 1.f);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

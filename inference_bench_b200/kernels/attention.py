@@ -55,6 +55,13 @@ L.register("ib_attention_decode_fused", [L._p, L._i, L._ll, L._p, L._p, L._f, L.
                                          L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
 L.register("ib_attention_prefill_tc", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
 L.register("ib_attention_prefill_ws", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._ll, L._p, L._p])
+# the same with capped scores and a sink (softcap, sink before the status word)
+L.register("ib_attention_decode_capped", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._f, L._i, L._p, L._p])
+L.register("ib_attention_decode_stream_capped", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._f, L._i,
+                                                 L._p, L._p])
+L.register("ib_attention_prefill_ws_capped", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._ll, L._f, L._i, L._p, L._p])
+L.KERNELS_PER_CALL["ib_attention_decode_capped"] = 2
+L.KERNELS_PER_CALL["ib_attention_decode_stream_capped"] = 2
 
 
 def has_tensor_core_kernel(dtype: torch.dtype, head_dim: int, heads: int, kv_heads: int) -> bool:
@@ -168,11 +175,16 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
     view = cache.c_view()
     qk_dim, v_dim = qk_dim or view.head_dim, v_dim or view.head_dim
     out = rt.empty((q.shape[0], heads * v_dim), q.dtype)
-    variant = softcap > 0 or sink or qk_dim != view.head_dim or v_dim != view.head_dim
-    if variant or not has_tensor_core_kernel(q.dtype, view.head_dim, heads, view.kv_heads):
+    capped = softcap > 0 or sink
+    generic = qk_dim != view.head_dim or v_dim != view.head_dim or not has_tensor_core_kernel(q.dtype, view.head_dim, heads, view.kv_heads)
+    work = None if generic else _work_lists(ctx)
+    if capped and not generic and work["n_tiles"] and (rt.options.prefill_attention == "tcgen05" or not cache.tma()[0]):
+        generic = True    # prompt portions with capped scores run on the kernel that TMA feeds, or on the generic one
+    if generic:
         ops.attention_generic(q, cache, ctx.positions, ctx.seg_of_token, window, scale, out, heads, rt.status, qk_dim, v_dim, softcap, sink)
         return out
-    work = _work_lists(ctx)
+    extra = (float(softcap), 1 if sink else 0) if capped else ()
+    tail = "_capped" if capped else ""
     stream = ops._stream()
     if work["n_dec"]:
         limit = view.table_stride * view.page_size
@@ -195,9 +207,9 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
         args = (q.data_ptr(), C.byref(view), work["dec_tokens"].data_ptr(), work["n_dec"], ctx.positions.data_ptr(), ctx.seg_of_token.data_ptr(),
                 int(window or 0), float(scale), part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), heads, max_slices, tps)
         if stream_map:
-            L.call("ib_attention_decode_stream", *args, stream_map, stream_row0, rt.status.data_ptr(), stream)
+            L.call("ib_attention_decode_stream" + tail, *args, stream_map, stream_row0, *extra, rt.status.data_ptr(), stream)
         else:
-            L.call("ib_attention_decode", *args, rt.status.data_ptr(), stream)
+            L.call("ib_attention_decode" + tail, *args, *extra, rt.status.data_ptr(), stream)
     if work["n_tiles"]:
         args = (q.data_ptr(), C.byref(view), work["tile_seg"].data_ptr(), work["tile_row0"].data_ptr(), work["n_tiles"], ctx.seg_start.data_ptr(),
                 ctx.seg_pos0.data_ptr(), int(window or 0), float(scale), out.data_ptr(), heads)
@@ -205,7 +217,7 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
         if rt.options.prefill_attention == "ws" and not kv_map:
             raise L.KernelError(f"prefill_attention = \"ws\" needs a page size that TMA can serve (a multiple of 8 that divides 64, or a multiple of 64), got {view.page_size}")
         if kv_map:
-            L.call("ib_attention_prefill_ws", *args, kv_map, row0, rt.status.data_ptr(), stream)
+            L.call("ib_attention_prefill_ws" + tail, *args, kv_map, row0, *extra, rt.status.data_ptr(), stream)
         else:
             L.call("ib_attention_prefill_tc", *args, rt.status.data_ptr(), stream)
     return out
