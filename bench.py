@@ -423,7 +423,59 @@ DESIGN_KINDS = {   # kinds of kernel by the library entry points that launch the
                 "heads": ["ib_gemm_heads", "ib_gemm_heads_mma"], "route": ["ib_moe_route", "ib_moe_sort", "ib_moe_combine"],
                 "norm": ["ib_norm_residual", "ib_latent_prepare", "ib_cast_rows"], "gemm": LEAVE_OUT["gemm"]},
     "qwen3": {"attention": LEAVE_OUT["attention"], "norm": LEAVE_OUT["norm"] + LEAVE_OUT["qk"], "gemm": LEAVE_OUT["gemm"] + LEAVE_OUT["qkv"]},
+    "busadra": {"attention": ["ib_attention_generic", "ib_attention_decode_capped", "ib_attention_decode_stream_capped", "ib_attention_prefill_ws_capped"],
+                "recurrence": ["ib_gated_recurrence", "ib_head_rmsnorm"],
+                "experts": ["ib_gemm_grouped", "ib_gemm_grouped_mma", "ib_gemm_grouped_tcgen05", "ib_gemm_grouped_swiglu_tcgen05", "ib_scatter_scaled_rows"],
+                "route": ["ib_moe_route", "ib_moe_sort", "ib_moe_combine"],
+                "norm": ["ib_add_layernorm", "ib_causal_conv_rows", "ib_depth_average", "ib_qk_norm_rope_kv"], "gemm": LEAVE_OUT["gemm"]},
 }
+# Busadra at layer sizes that resemble small hybrid models: windowed grouped-query attention with heads of 128, a gated linear recurrence
+# whose heads hold a 128 x 128 state, and routed experts; layers in the order attention, recurrence, recurrence, attention (repeated).
+BUSADRA_SIZES = {
+    "small": dict(width=1024, heads=8, kv_heads=2, dim=128, window=1024, rec_heads=8, rec_dim=128, rec_vdim=128, experts=16, top=2, expert_ff=1024, vocab=32768),
+    "mid": dict(width=2048, heads=16, kv_heads=4, dim=128, window=2048, rec_heads=16, rec_dim=128, rec_vdim=128, experts=64, top=6, expert_ff=1408, vocab=32768),
+}
+
+
+def busadra_config(z: dict, layers: int) -> dict:
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "mask": {"size": z["window"]}, "scale": z["dim"] ** -0.5, "softcap": 30.0,
+           "rot": {"base": 500000.0, "dims": z["dim"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    rec = {"heads": z["rec_heads"], "dim": z["rec_dim"], "vdim": z["rec_vdim"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    ls = [{"type": "attention", "mixer": att, "mlp": moe} if i % 4 in (0, 3) else {"type": "hgrn2", "mixer": rec, "mlp": moe} for i in range(layers)]
+    return {"architecture": "Busadra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "logit_scale": 1.0, "layers": ls}
+
+
+def qwen3_like_busadra(z: dict, layers: int) -> dict:
+    """The Qwen3 shape of equal width, heads, kv heads, head size and active feed-forward size, every layer windowed like the design's attention."""
+    return dict(QWEN3_8B, vocab_size=z["vocab"], hidden_size=z["width"], num_hidden_layers=layers, num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+                head_dim=z["dim"], intermediate_size=z["top"] * z["expert_ff"], use_sliding_window=True, sliding_window=z["window"], max_window_layers=0,
+                layer_types=["sliding_attention"] * layers)
+
+
+def busadra_work(z: dict, layers: int, T: int, ctx: int, batch: int) -> dict:
+    """Algorithmic FLOPs and bytes of the design's own kinds of kernel, for a prefill of T tokens and for a decode step of `batch` requests
+    at `ctx` tokens of context (per step, all layers). The recurrence's products are float32 FMAs, not tensor-core work: its floor is
+    given in bytes only (the projections it reads and, per decoded token, the state's trip from memory and back)."""
+    n_att = sum(1 for i in range(layers) if i % 4 in (0, 3))
+    n_rec = layers - n_att
+    H, G, D, W = z["heads"], z["kv_heads"], z["dim"], z["window"]
+    pairs = sum(min(t + 1, W) for t in range(T))
+    seen = min(ctx, W)
+    rh, rd, rv = z["rec_heads"], z["rec_dim"], z["rec_vdim"]
+    width = z["width"]
+    norm_bytes = lambda rows: layers * rows * width * (2 * (4 + 4 + 4 + 4 + 4 + 2) + (4 + 4 + 4 + 4 * (layers / 2 + 1)))   # two norms and convolutions, the depth average
+    return {
+        "prefill": {"attention": {"flops": n_att * 4.0 * H * D * pairs},
+                    "recurrence": {"flops": 0.0, "bytes": n_rec * T * rh * (4.0 * (2 * rd + rv) + 4.0 * rv + 6.0 * rv)},
+                    "experts": {"flops": layers * 2.0 * T * z["top"] * 3 * z["expert_ff"] * width},
+                    "norm": {"flops": 0.0, "bytes": norm_bytes(T)}},
+        "decode": {"attention": {"flops": n_att * 4.0 * H * D * batch * seen, "bytes": n_att * 2.0 * batch * seen * G * 2 * D},
+                   "recurrence": {"flops": 0.0, "bytes": n_rec * batch * rh * (8.0 * rd * rv + 4.0 * (2 * rd + rv) + 10.0 * rv)},
+                   "experts": {"flops": layers * 2.0 * batch * z["top"] * 3 * z["expert_ff"] * width,
+                               "bytes": layers * 2.0 * min(batch * z["top"], z["experts"]) * 3 * z["expert_ff"] * width},
+                   "norm": {"flops": 0.0, "bytes": norm_bytes(batch)}},
+    }
 
 
 def kernel_times(engine, entries) -> dict:
@@ -493,8 +545,14 @@ def design_work(z: dict, layers: int, T: int, ctx: int, batch: int) -> dict:
 
 def qwen3_work(cfg: dict, layers: int, T: int, ctx: int, batch: int) -> dict:
     q = cfg["num_attention_heads"] * cfg["head_dim"]
-    return {"prefill": {"attention": {"flops": layers * 4.0 * (T * (T + 1) / 2) * q}},
-            "decode": {"attention": {"flops": layers * 4.0 * batch * ctx * q, "bytes": batch * ctx * kv_bytes_per_token(cfg, layers)}}}
+    W = cfg.get("sliding_window") if cfg.get("use_sliding_window") else None
+    pairs = T * (T + 1) / 2 if not W else sum(min(t + 1, W) for t in range(T))
+    seen = ctx if not W else min(ctx, W)
+    width = cfg["hidden_size"]
+    norm_bytes = lambda rows: layers * rows * (2 * width * (4 + 4 + 4 + 2) + (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"] * (4 + 2))
+    return {"prefill": {"attention": {"flops": layers * 4.0 * pairs * q}, "norm": {"flops": 0.0, "bytes": norm_bytes(T)}},
+            "decode": {"attention": {"flops": layers * 4.0 * batch * seen * q, "bytes": batch * seen * kv_bytes_per_token(cfg, layers)},
+                       "norm": {"flops": 0.0, "bytes": norm_bytes(batch)}}}
 
 
 def run_design(args) -> dict:
@@ -510,11 +568,14 @@ def run_design(args) -> dict:
     pk, pk_src = peaks()
     layers = args.layers or 4
     steps, warmup = min(args.steps, 32), max(args.warmup, 3)
-    out = {"design": "zabonex", "layers": layers, "peaks": pk_src, "sizes": {}}
-    for name in (args.size.split(",") if args.size else list(DESIGN_SIZES)):
-        z = DESIGN_SIZES[name]
+    out = {"design": args.design, "layers": layers, "peaks": pk_src, "sizes": {}}
+    sizes = BUSADRA_SIZES if args.design == "busadra" else DESIGN_SIZES
+    for name in (args.size.split(",") if args.size else list(sizes)):
+        z = sizes[name]
         report = {}
-        for arch, cfg in (("zabonex", zabonex_config(z, layers)), ("qwen3", qwen3_like(z, layers))):
+        pair = (("busadra", busadra_config(z, layers)), ("qwen3", qwen3_like_busadra(z, layers))) if args.design == "busadra" else \
+            (("zabonex", zabonex_config(z, layers)), ("qwen3", qwen3_like(z, layers)))
+        for arch, cfg in pair:
             engine = Engine(cfg, dtype="bfloat16", max_ctx=CONTEXT, page_size=PAGE_ENGINE, num_pages=64 * (CONTEXT // PAGE_ENGINE) + 64, max_num_seqs=64,
                             max_batched_tokens=8192, prefill_chunk=PROMPT, random_weights_seed=0)
             vocab = engine.decoder.plan.vocab_size
@@ -522,6 +583,11 @@ def run_design(args) -> dict:
                 work = design_work(z, layers, PROMPT, PROMPT, 8)
                 lin = layers * (z["heads"] * (z["dim"] + z["rot"]) + z["heads"] * z["vdim"]) * z["width"] + (layers + 1) // 2 * (z["rank"] + z["rot"]) * z["width"] + \
                     3 * z["dense_ff"] * z["width"] + (layers - 1) * (3 * z["shared_ff"] + z["experts"]) * z["width"] + vocab * z["width"]
+            elif arch == "busadra":
+                work = busadra_work(z, layers, PROMPT, PROMPT, 8)
+                n_att = sum(1 for i in range(layers) if i % 4 in (0, 3))
+                lin = n_att * (2 * z["heads"] + 2 * z["kv_heads"]) * z["dim"] * z["width"] + \
+                    (layers - n_att) * z["rec_heads"] * (2 * z["rec_dim"] + 2 * z["rec_vdim"]) * z["width"] + layers * z["experts"] * z["width"] + vocab * z["width"]
             else:
                 work = qwen3_work(cfg, layers, PROMPT, PROMPT, 8)
                 lin = weight_bytes(cfg, layers) // 2
@@ -587,8 +653,8 @@ def main() -> int:
     ap.add_argument("--leave-out", default="", help="with --only decode or prefill: also time the step without each of these kinds of kernel (comma separated; "
                     "a+b leaves both out): " + ", ".join(sorted(LEAVE_OUT)))
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "mixed"], help="run one part alone (for profiling); prints a short report")
-    ap.add_argument("--design", default="", choices=["", "zabonex"], help="measure another design beside the Qwen3 shape of equal size instead of the benchmark (prints its own report)")
-    ap.add_argument("--size", default="", help="with --design: which of its sizes (comma separated; default all): " + ", ".join(DESIGN_SIZES))
+    ap.add_argument("--design", default="", choices=["", "zabonex", "busadra"], help="measure another design beside the Qwen3 shape of equal size instead of the benchmark (prints its own report)")
+    ap.add_argument("--size", default="", help="with --design: which of its sizes (comma separated; default all): " + ", ".join(DESIGN_SIZES) + " (zabonex); " + ", ".join(BUSADRA_SIZES) + " (busadra)")
     args = ap.parse_args()
     if args.design:
         print(json.dumps(run_design(args)))

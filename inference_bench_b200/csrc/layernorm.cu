@@ -74,7 +74,11 @@ template <typename O>
 __global__ void __launch_bounds__(kLnThreads) causal_conv_rows_kernel(const float* __restrict__ ext, const float* __restrict__ w, int taps, O* __restrict__ out,
                                                                       int T, int H, const int* __restrict__ seg_of_token, const int* __restrict__ seg_start,
                                                                       const int* __restrict__ seg_slot, float* __restrict__ state, size_t slot_stride) {
-  ib::pdl_launch_dependents();
+  // This kernel does not let its dependents start early. What follows it is a sublayer's first matrix product, which takes its tensor
+  // memory before it waits; the product two kernels back (a mixer's output projection) may itself still be waiting for tensor memory
+  // that an attention kernel holds, and a later, smaller request must not be served before it: the later kernel would then hold what
+  // the earlier one needs while waiting for it. With no early start here, nothing after this kernel runs before the products before it
+  // are done.
   ib::pdl_wait();
   const int halo = taps - 1;
   const int b = blockIdx.x;
@@ -102,7 +106,8 @@ __global__ void __launch_bounds__(kLnThreads) causal_conv_rows_kernel(const floa
 
 __global__ void depth_average_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride, const float* __restrict__ dscale,
                                      const float* __restrict__ dbias, float* __restrict__ stack, size_t layer_stride, int k, const float* __restrict__ mix, int H) {
-  ib::pdl_launch_dependents();
+  // (no early start of the dependents, for the reason given in causal_conv_rows_kernel: in a layer without a feed-forward this kernel
+  // is what stands between a mixer's output projection and the next matrix product)
   ib::pdl_wait();
   const size_t t = blockIdx.y;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) {
