@@ -424,7 +424,7 @@ DESIGN_KINDS = {   # kinds of kernel by the library entry points that launch the
                 "norm": ["ib_norm_residual", "ib_latent_prepare", "ib_cast_rows"], "gemm": LEAVE_OUT["gemm"]},
     "qwen3": {"attention": LEAVE_OUT["attention"], "norm": LEAVE_OUT["norm"] + LEAVE_OUT["qk"], "gemm": LEAVE_OUT["gemm"] + LEAVE_OUT["qkv"]},
     "busadra": {"attention": ["ib_attention_generic", "ib_attention_decode_capped", "ib_attention_decode_stream_capped", "ib_attention_prefill_ws_capped"],
-                "recurrence": ["ib_gated_recurrence", "ib_head_rmsnorm"],
+                "recurrence": ["ib_gated_recurrence", "ib_recurrence_chunks_finish", "ib_head_rmsnorm"],
                 "experts": ["ib_gemm_grouped", "ib_gemm_grouped_mma", "ib_gemm_grouped_tcgen05", "ib_gemm_grouped_swiglu_tcgen05", "ib_scatter_scaled_rows"],
                 "route": ["ib_moe_route", "ib_moe_sort", "ib_moe_combine"],
                 "norm": ["ib_add_layernorm", "ib_causal_conv_rows", "ib_depth_average", "ib_qk_norm_rope_kv"], "gemm": LEAVE_OUT["gemm"]},

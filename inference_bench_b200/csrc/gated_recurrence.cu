@@ -7,6 +7,11 @@
 //    the tokens of the segment are walked in order, sixteen at a time: the CTA first turns the sixteen tokens' projections into q, f
 //    and 1 - f in shared memory, then every thread updates its rows and adds its share of o[j], which a shuffle sums over the DS
 //    threads of the column. A decoded token is a segment of one: the cost is then the state's trip from memory and back.
+//    With `chunks` the same kernel walks chunks of a long segment instead, each from a zero state: it leaves the chunk's own
+//    outputs, its closing state and decay, and q_t times the decay from the chunk's start to t; `chunk_carry` then walks a segment's
+//    chunks in order (S_in of the next = decay * S_in + the chunk's closing state, elementwise, ending in the request's state) and
+//    `chunk_apply` adds (q_t * decay)^T S_in to every output. The three give what the walk over the whole segment gives, up to
+//    rounding, with as many CTAs as the segment has chunks; which path a segment takes depends on its own length only.
 //  * head_rmsnorm: out[t, a, :] = w * o[t, a, :] / sqrt(mean(o^2) + eps), into the activation dtype.
 #include <type_traits>
 
@@ -20,23 +25,38 @@ constexpr int kChunk = 16;   // tokens prepared at a time
 template <int RPT, int kCols>
 __global__ void __launch_bounds__(kCols * 32) gated_recurrence_kernel(const float* __restrict__ proj, int P, size_t stride_p, int R, const float* __restrict__ f_bias,
                                         const float* __restrict__ lower, float* __restrict__ state, size_t slot_stride, const int* __restrict__ seg_start,
-                                        const int* __restrict__ seg_slot, float* __restrict__ o_out, int heads, int D, int V, int DS) {
-  extern __shared__ float sm[];   // q[kChunk][D], f[kChunk][D], g[kChunk][D], v[kChunk][kCols]
+                                        const int* __restrict__ seg_slot, float* __restrict__ o_out, int heads, int D, int V, int DS,
+                                        const int* __restrict__ seg_list, const int* __restrict__ chunks, float* __restrict__ chunk_state,
+                                        float* __restrict__ chunk_decay, float* __restrict__ qa_out) {
+  // seg_list: the segments this launch walks (null: all). chunks != null: blockIdx.x is a chunk (first row, rows) that starts from a zero
+  // state and leaves its closing state in chunk_state[chunk][head], its decay in chunk_decay[chunk][head] and q * decay in qa_out[row][head].
+  extern __shared__ float sm[];   // q[kChunk][D], f[kChunk][D], g[kChunk][D], v[kChunk][kCols], running decay [D]
   float* sq = sm;
   float* sf = sq + kChunk * D;
   float* sg = sf + kChunk * D;
   float* sv = sg + kChunk * D;
+  float* run = sv + kChunk * kCols;
   ib::pdl_launch_dependents();
   ib::pdl_wait();
-  const int s = blockIdx.x, a = blockIdx.y, j0 = blockIdx.z * kCols;
+  const int a = blockIdx.y, j0 = blockIdx.z * kCols;
   const int tid = threadIdx.x, ds = tid % DS, col = tid / DS, j = j0 + col;
-  const int t0 = seg_start[s], t1 = seg_start[s + 1];
-  float* S = state + (size_t)seg_slot[s] * slot_stride + (size_t)a * D * V;
+  int t0, t1;
+  float* S;
+  if (chunks) {
+    t0 = chunks[2 * blockIdx.x];
+    t1 = t0 + chunks[2 * blockIdx.x + 1];
+    S = chunk_state + ((size_t)blockIdx.x * heads + a) * D * V;
+    for (int d = tid; d < D; d += blockDim.x) run[d] = 1.f;
+  } else {
+    const int s = seg_list ? seg_list[blockIdx.x] : blockIdx.x;
+    t0 = seg_start[s], t1 = seg_start[s + 1];
+    S = state + (size_t)seg_slot[s] * slot_stride + (size_t)a * D * V;
+  }
   float st[RPT];
 #pragma unroll
   for (int r = 0; r < RPT; r++) {
     const int d = ds + r * DS;
-    st[r] = (d < D && j < V) ? S[(size_t)d * V + j] : 0.f;
+    st[r] = (!chunks && d < D && j < V) ? S[(size_t)d * V + j] : 0.f;
   }
   const int q_off = a * D, f_off = heads * D + a * D, v_off = 2 * heads * D + a * V + j0;
   for (int c0 = t0; c0 < t1; c0 += kChunk) {
@@ -66,6 +86,16 @@ __global__ void __launch_bounds__(kCols * 32) gated_recurrence_kernel(const floa
       sv[i] = z;
     }
     __syncthreads();
+    if (chunks && blockIdx.z == 0) {   // q times the decay since the chunk's start, for the pass that adds the incoming state's share
+      for (int d = tid; d < D; d += blockDim.x) {
+        float r = run[d];
+        for (int tt = 0; tt < n; tt++) {
+          r *= sf[tt * D + d];
+          qa_out[((size_t)(c0 + tt) * heads + a) * D + d] = sq[tt * D + d] * r;
+        }
+        run[d] = r;
+      }
+    }
     for (int tt = 0; tt < n; tt++) {
       const float vj = sv[tt * kCols + col];
       const float* fq = sq + tt * D;
@@ -89,6 +119,73 @@ __global__ void __launch_bounds__(kCols * 32) gated_recurrence_kernel(const floa
     const int d = ds + r * DS;
     if (d < D && j < V) S[(size_t)d * V + j] = st[r];
   }
+  if (chunks && blockIdx.z == 0) {
+    __syncthreads();
+    for (int d = tid; d < D; d += blockDim.x) chunk_decay[((size_t)blockIdx.x * heads + a) * D + d] = run[d];
+  }
+}
+
+// One thread per element (d, j) of a head's state walks a long segment's chunks in order: the chunk's place in chunk_state receives
+// the state the chunk starts from, and the request's state slot the state after the last chunk.
+__global__ void chunk_carry_kernel(const int* __restrict__ long_segs, const int* __restrict__ seg_slot, float* __restrict__ state, size_t slot_stride,
+                                   float* __restrict__ chunk_state, const float* __restrict__ chunk_decay, int heads, int D, int V) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int s = long_segs[3 * blockIdx.x], c_first = long_segs[3 * blockIdx.x + 1], n_chunks = long_segs[3 * blockIdx.x + 2];
+  const int a = blockIdx.y;
+  float* S = state + (size_t)seg_slot[s] * slot_stride + (size_t)a * D * V;
+  for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < D * V; e += gridDim.z * blockDim.x) {
+    const int d = e / V;
+    float cur = S[e];
+    for (int c = c_first; c < c_first + n_chunks; c++) {
+      float* slot = chunk_state + ((size_t)c * heads + a) * D * V + e;
+      const float own = *slot;
+      *slot = cur;
+      cur = __fmaf_rn(chunk_decay[((size_t)c * heads + a) * D + d], cur, own);
+    }
+    S[e] = cur;
+  }
+}
+
+// o[t][j] += sum_d qa[t][d] * S_in[d][j] for the rows of one chunk: a CTA of 256 threads takes 64 rows x 32 columns, 32 values of d at a time.
+__global__ void __launch_bounds__(256) chunk_apply_kernel(const int* __restrict__ chunks, const float* __restrict__ chunk_state, const float* __restrict__ qa,
+                                                          float* __restrict__ o_out, int heads, int D, int V) {
+  __shared__ float s_in[32][33];
+  __shared__ float s_q[64][33];
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int t0 = chunks[2 * blockIdx.x], n = chunks[2 * blockIdx.x + 1];
+  const int a = blockIdx.y, j0 = blockIdx.z * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const float* Sin = chunk_state + ((size_t)blockIdx.x * heads + a) * D * V;
+  float acc[8];
+#pragma unroll
+  for (int r = 0; r < 8; r++) acc[r] = 0.f;
+  for (int d0 = 0; d0 < D; d0 += 32) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * 32; i += 256) {
+      const int dd = i >> 5, c = i & 31;
+      s_in[dd][c] = (d0 + dd < D && j0 + c < V) ? Sin[(size_t)(d0 + dd) * V + j0 + c] : 0.f;
+    }
+    for (int i = threadIdx.x; i < 64 * 32; i += 256) {
+      const int tt = i >> 5, dd = i & 31;
+      s_q[tt][dd] = (tt < n && d0 + dd < D) ? qa[((size_t)(t0 + tt) * heads + a) * D + d0 + dd] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int dd = 0; dd < 32; dd++) {
+      const float sv = s_in[dd][tx];
+#pragma unroll
+      for (int r = 0; r < 8; r++) acc[r] = __fmaf_rn(s_q[ty * 8 + r][dd], sv, acc[r]);
+    }
+  }
+  if (j0 + tx < V) {
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      const int tt = ty * 8 + r;
+      if (tt < n) o_out[((size_t)(t0 + tt) * heads + a) * V + j0 + tx] += acc[r];
+    }
+  }
 }
 
 template <typename O>
@@ -107,9 +204,15 @@ __global__ void head_rmsnorm_kernel(const float* __restrict__ o, const float* __
 
 }  // namespace
 
+// seg_list: int32 [n_segments] of the segments to walk (null: segments 0 .. n_segments - 1).
+// chunks: null, or int32 [n_segments][2] = (first row, rows <= 64) of chunks that each start from a zero state (n_segments then counts
+// chunks); chunk_state float32 [chunks][heads][D][V], chunk_decay float32 [chunks][heads][D] and qa float32 [T][heads][D] receive what
+// ib_recurrence_chunks_finish needs.
 extern "C" int ib_gated_recurrence(const float* proj, int P, long long stride_p, const float* f_bias, const float* lower, float* state, long long slot_stride,
-                                   const int* seg_start, const int* seg_slot, int n_segments, float* o_out, int heads, int D, int V, cudaStream_t stream) {
+                                   const int* seg_start, const int* seg_slot, int n_segments, float* o_out, int heads, int D, int V, const int* seg_list,
+                                   const int* chunks, float* chunk_state, float* chunk_decay, float* qa, cudaStream_t stream) {
   if (n_segments == 0) return 0;
+  IB_CHECK_ARG(!chunks || (chunk_state && chunk_decay && qa), "gated_recurrence: chunks need their state, decay and query buffers");
   IB_CHECK_ARG(n_segments > 0 && P >= 1 && heads > 0 && D > 0 && V > 0, "gated_recurrence: bad sizes segments=%d P=%d heads=%d D=%d V=%d", n_segments, P, heads, D, V);
   IB_CHECK_ARG(D <= 512, "gated_recurrence: a head's key size %d is above 512", D);
   const int rpt = D <= 256 ? 8 : 16, kCols = D <= 256 ? 32 : 16;
@@ -117,15 +220,29 @@ extern "C" int ib_gated_recurrence(const float* proj, int P, long long stride_p,
   int DS = 1;
   while (DS * rpt < D) DS *= 2;
   const int R = 2 * heads * D + heads * V;
-  const size_t smem = (size_t)kChunk * (3 * D + kCols) * sizeof(float);
+  const size_t smem = ((size_t)kChunk * (3 * D + kCols) + D) * sizeof(float);
   const dim3 grid((unsigned)n_segments, (unsigned)heads, (unsigned)((V + kCols - 1) / kCols));
   auto go = [&](auto kernel) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ib::launch(kernel, grid, kCols * DS, smem, stream, proj, P, (size_t)stride_p, R, f_bias, lower, state, (size_t)slot_stride, seg_start, seg_slot, o_out, heads, D, V, DS);
+    ib::launch(kernel, grid, kCols * DS, smem, stream, proj, P, (size_t)stride_p, R, f_bias, lower, state, (size_t)slot_stride, seg_start, seg_slot, o_out, heads, D, V, DS,
+               seg_list, chunks, chunk_state, chunk_decay, qa);
   };
   if (rpt == 8) go(gated_recurrence_kernel<8, 32>);
   else go(gated_recurrence_kernel<16, 16>);
   IB_CHECK_LAUNCH("gated_recurrence");
+  return 0;
+}
+
+// After ib_gated_recurrence on chunks: long_segs int32 [n_long][3] = (segment, its first chunk, its chunks), chunks as above (n_chunks of them).
+extern "C" int ib_recurrence_chunks_finish(const int* long_segs, int n_long, const int* chunks, int n_chunks, const int* seg_slot, float* state, long long slot_stride,
+                                           float* chunk_state, const float* chunk_decay, const float* qa, float* o_out, int heads, int D, int V, cudaStream_t stream) {
+  if (n_long == 0 || n_chunks == 0) return 0;
+  IB_CHECK_ARG(n_long > 0 && n_chunks > 0 && heads > 0 && heads <= 65535 && D > 0 && V > 0, "recurrence_chunks_finish: bad sizes");
+  ib::launch(chunk_carry_kernel, dim3((unsigned)n_long, (unsigned)heads, (unsigned)min((D * V + 255) / 256, 64)), 256, 0, stream, long_segs, seg_slot, state,
+             (size_t)slot_stride, chunk_state, chunk_decay, heads, D, V);
+  IB_CHECK_LAUNCH("recurrence chunk_carry");
+  ib::launch(chunk_apply_kernel, dim3((unsigned)n_chunks, (unsigned)heads, (unsigned)((V + 31) / 32)), 256, 0, stream, chunks, (const float*)chunk_state, qa, o_out, heads, D, V);
+  IB_CHECK_LAUNCH("recurrence chunk_apply");
   return 0;
 }
 

@@ -592,14 +592,21 @@ def scale_values(v: torch.Tensor, s: float) -> None:
 
 
 # ---------------------------------------------------------------- gated linear recurrence (csrc/gated_recurrence.cu)
-L.register("ib_gated_recurrence", [L._p, L._i, L._ll, L._p, L._p, L._p, L._ll, L._p, L._p, L._i, L._p, L._i, L._i, L._i, L._p])
+L.register("ib_gated_recurrence", [L._p, L._i, L._ll, L._p, L._p, L._p, L._ll, L._p, L._p, L._i, L._p, L._i, L._i, L._i, L._p, L._p, L._p, L._p, L._p, L._p])
+L.register("ib_recurrence_chunks_finish", [L._p, L._i, L._p, L._i, L._p, L._p, L._ll, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._p])
+L.KERNELS_PER_CALL["ib_recurrence_chunks_finish"] = 2
+RECURRENCE_CHUNK = 64   # rows of a chunk of the chunked form (csrc/gated_recurrence.cu: chunk_apply takes 64 rows a CTA)
 L.register("ib_head_rmsnorm", [L._p, L._p, L._f, L._p, L._i, L._ll, L._i, L._p])
 
 
 def gated_recurrence(proj: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor,
-                     n_segments: int, out: torch.Tensor, heads: int, dim: int, vdim: int) -> None:
+                     n_segments: int, out: torch.Tensor, heads: int, dim: int, vdim: int, seg_list: Optional[torch.Tensor] = None,
+                     long_segs: Optional[torch.Tensor] = None, chunks: Optional[torch.Tensor] = None) -> None:
     """proj float32 [P, T, heads * (2 dim + vdim)] = partial sums of [q | f | v]; state float32 [slots, heads, dim, vdim], advanced in place for the
-    step's segments; out float32 [T, heads, vdim] = S^T q after every token."""
+    step's segments; out float32 [T, heads, vdim] = S^T q after every token.
+    seg_list (int32 [n]): walk only these segments, token by token. long_segs (int32 [n, 3] of (segment, first chunk, chunks)) with chunks
+    (int32 [m, 2] of (first row, rows <= RECURRENCE_CHUNK)): these segments in the chunked form instead (every chunk alone from a zero
+    state, then the states carried from chunk to chunk, then each chunk's incoming state applied to its rows)."""
     _check("proj", proj, torch.float32)
     P, T, R = proj.shape
     if R != heads * (2 * dim + vdim):
@@ -612,8 +619,25 @@ def gated_recurrence(proj: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tens
     _check("out", out, torch.float32, (T, heads, vdim))
     _check("seg_start", seg_start, torch.int32)
     _check("seg_slot", seg_slot, torch.int32)
-    L.call("ib_gated_recurrence", proj.data_ptr(), P, T * R, f_bias.data_ptr(), lower.data_ptr(), state.data_ptr(), heads * dim * vdim, seg_start.data_ptr(),
-           seg_slot.data_ptr(), n_segments, out.data_ptr(), heads, dim, vdim, _stream())
+    common = (proj.data_ptr(), P, T * R, f_bias.data_ptr(), lower.data_ptr(), state.data_ptr(), heads * dim * vdim, seg_start.data_ptr(), seg_slot.data_ptr())
+    if long_segs is None:
+        if seg_list is not None:
+            _check("seg_list", seg_list, torch.int32)
+            n_segments = seg_list.shape[0]
+        L.call("ib_gated_recurrence", *common, n_segments, out.data_ptr(), heads, dim, vdim, _ptr(seg_list), None, None, None, None, _stream())
+        return
+    _check("long_segs", long_segs, torch.int32)
+    _check("chunks", chunks, torch.int32)
+    if seg_list is not None and seg_list.shape[0]:
+        L.call("ib_gated_recurrence", *common, seg_list.shape[0], out.data_ptr(), heads, dim, vdim, seg_list.data_ptr(), None, None, None, None, _stream())
+    m = chunks.shape[0]
+    chunk_state = torch.empty((m, heads, dim, vdim), dtype=torch.float32, device=proj.device)
+    chunk_decay = torch.empty((m, heads, dim), dtype=torch.float32, device=proj.device)
+    qa = torch.empty((T, heads, dim), dtype=torch.float32, device=proj.device)
+    L.call("ib_gated_recurrence", *common, m, out.data_ptr(), heads, dim, vdim, None, chunks.data_ptr(), chunk_state.data_ptr(), chunk_decay.data_ptr(), qa.data_ptr(),
+           _stream())
+    L.call("ib_recurrence_chunks_finish", long_segs.data_ptr(), long_segs.shape[0], chunks.data_ptr(), m, seg_slot.data_ptr(), state.data_ptr(), heads * dim * vdim,
+           chunk_state.data_ptr(), chunk_decay.data_ptr(), qa.data_ptr(), out.data_ptr(), heads, dim, vdim, _stream())
 
 
 def head_rmsnorm(o: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:

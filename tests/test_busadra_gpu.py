@@ -262,6 +262,26 @@ def test_recurrence_over_portions_slots_and_long_decoding(rt32, heads, D, V):
     plan = [[("a", 1), ("b", 2)], [("a", 2), ("b", 17)], [("b", 22), ("a", 40)], [("c", 3), ("a", 17)], [("c", 17)]] + [[("a", 1)]] * 150
     slot, at = {"a": 0, "b": 1, "c": 1}, {r: 0 for r in lens}
     worst = 0.0
+    # the chunked form of long segments: both requests whole in one step (210 and 41 rows: one goes in chunks, the other token by token), then
+    # a second long portion on top of a state that is not zero
+    for step in ([("a", 210), ("b", 41)], [("a", 70), ("b", 2)], [("a", 140), ("b", 39)]):
+        if step[0][1] != 140:
+            st2 = torch.zeros((3, heads, D, V), device=DEV)
+            at2 = {r: 0 for r in lens}
+        from inference_bench_b200.parts.recurrent import GatedLinearRecurrence
+        ctx = _ctx(rt32, [(at2[r], n) for r, n in step], [slot[r] for r, _ in step])
+        short, long_segs, chunks = GatedLinearRecurrence._cut(ctx)
+        assert long_segs is not None and long_segs.shape[0] == 1 and short.tolist() == [1]
+        pr = torch.cat([proj[r][:, at2[r]:at2[r] + n] for r, n in step], dim=1).to(DEV).contiguous()
+        o = torch.empty((pr.shape[1], heads, V), device=DEV)
+        ops.gated_recurrence(pr, _f32(f_bias), _f32(lower), st2, ctx.seg_start, ctx.seg_slot, len(step), o, heads, D, V, seg_list=short, long_segs=long_segs, chunks=chunks)
+        k = 0
+        for r, n in step:
+            err = (o[k:k + n].cpu().double() - want[r][at2[r]:at2[r] + n]).abs().max().item()
+            assert err < 2e-4 * max(1.0, want[r].abs().max().item()), f"chunked form, request {r} rows {at2[r]}..{at2[r] + n}: {err}"
+            k, at2[r] = k + n, at2[r] + n
+        if at2["a"] == 210:
+            assert torch.allclose(st2[0].cpu().double(), want_state["a"], atol=1e-4) and torch.allclose(st2[1].cpu().double(), want_state["b"], atol=1e-4)
     for step in plan:
         if step[0][0] == "c" and at["c"] == 0:
             assert torch.allclose(state[1].cpu().double(), want_state["b"], atol=1e-4)
