@@ -137,11 +137,24 @@ __global__ void chunk_carry_kernel(const int* __restrict__ long_segs, const int*
   for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < D * V; e += gridDim.z * blockDim.x) {
     const int d = e / V;
     float cur = S[e];
-    for (int c = c_first; c < c_first + n_chunks; c++) {
-      float* slot = chunk_state + ((size_t)c * heads + a) * D * V + e;
-      const float own = *slot;
-      *slot = cur;
-      cur = __fmaf_rn(chunk_decay[((size_t)c * heads + a) * D + d], cur, own);
+    for (int c0 = c_first; c0 < c_first + n_chunks; c0 += 8) {   // eight chunks' values are requested before the first is used
+      float own[8], dec[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int c = c0 + u;
+        if (c < c_first + n_chunks) {
+          own[u] = chunk_state[((size_t)c * heads + a) * D * V + e];
+          dec[u] = chunk_decay[((size_t)c * heads + a) * D + d];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int c = c0 + u;
+        if (c < c_first + n_chunks) {
+          chunk_state[((size_t)c * heads + a) * D * V + e] = cur;
+          cur = __fmaf_rn(dec[u], cur, own[u]);
+        }
+      }
     }
     S[e] = cur;
   }

@@ -554,11 +554,11 @@ def add_layernorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tenso
 
 
 def causal_conv_rows(ext: torch.Tensor, w: torch.Tensor, out: torch.Tensor, layout: ConvLayout) -> None:
-    """out[t] = h[t] + sum_j w[:, j] h[t - taps + 1 + j] over a request's rows (ext: the normed rows in the layout of `ConvLayout`, taps =
-    halo + 1, w float32 [H, taps]); the request's state becomes the last `halo` rows of its run."""
+    """out[t] = h[t] + sum_j w[j] h[t - taps + 1 + j] over a request's rows (ext: the normed rows in the layout of `ConvLayout`, taps =
+    halo + 1, w float32 [taps, H]: a tap's weights for all channels lie together); the request's state becomes the last `halo` rows of its run."""
     T, H = out.shape
     _check("ext", ext, torch.float32, (layout.rows(T), H))
-    _check("w", w, torch.float32, (H, layout.halo + 1))
+    _check("w", w, torch.float32, (layout.halo + 1, H))
     _check("out", out)
     L.call("ib_causal_conv_rows", ext.data_ptr(), w.data_ptr(), layout.halo + 1, out.data_ptr(), dtype_code(out.dtype), T, H, layout.seg_of_token.data_ptr(),
            layout.seg_start.data_ptr(), layout.seg_slot.data_ptr(), layout.n_segments, layout.state.data_ptr(), layout.slot_stride, _stream())

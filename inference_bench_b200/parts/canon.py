@@ -55,9 +55,10 @@ class CanonBlock(base.Block, base.Part):
         return specs
 
     def bind(self, weights, rt):
-        self.ls1, self.conv1, self.mix = rt.vector(weights[self._n(0)]), rt.vector(weights[self._n(2)]), rt.vector(weights[self._n(4)])
+        # the convolution's taps are stored [channel, tap]; the kernel reads a tap's weights for neighbouring channels together: [tap, channel]
+        self.ls1, self.conv1, self.mix = rt.vector(weights[self._n(0)]), rt.vector(weights[self._n(2)].t()), rt.vector(weights[self._n(4)])
         if self.has_ff:
-            self.ls2, self.conv2 = rt.vector(weights[self._n(1)]), rt.vector(weights[self._n(3)])
+            self.ls2, self.conv2 = rt.vector(weights[self._n(1)]), rt.vector(weights[self._n(3)].t())
 
     def cache_need(self):
         own = FixedState((2, max(self.taps - 1, 1), self.hidden), torch.float32)   # [sublayer, row, channel]

@@ -61,7 +61,7 @@ def _ctx(rt, runs, slots=None):
 
 
 # ------------------------------------------------------------------------------------------ norm, convolution, state, depth average
-@pytest.mark.parametrize("H,taps", [(80, 3), (132, 1), (256, 5), (4096, 4), (24, 2)])
+@pytest.mark.parametrize("H,taps", [(80, 3), (132, 1), (256, 5), (4096, 4), (24, 2), (30, 3), (1022, 4)])
 def test_layer_norm_convolution_and_its_state_over_portions(rt32, H, taps):
     """Three requests in two slots (one slot is used again, zeroed, by the third) are fed in portions of 1, 2 and more tokens, also
     fewer than taps - 1, together in one batch; every row equals the plain norm and convolution of the whole sequence. The
@@ -96,7 +96,7 @@ def test_layer_norm_convolution_and_its_state_over_portions(rt32, H, taps):
         for dt, tol in ((torch.float32, 3e-5), (torch.bfloat16, 3e-2)):
             out = torch.empty((xs.shape[0], H), dtype=dt, device=DEV)
             saved = state.clone()
-            ops.causal_conv_rows(ext, _f32(cw), out, lay)
+            ops.causal_conv_rows(ext, _f32(cw.t()), out, lay)
             if dt == torch.float32:
                 state.copy_(saved)       # the second pass writes the same state again
             o = 0
