@@ -3,10 +3,11 @@
 // where z_q, z_f, v are the rows [q | f | v] of one fused projection (float32 partial sums, added in order). The state S [D, V] is
 // float32, lives in the request's state slot, starts at zero and is carried from token to token; everything here is float32.
 //
-//  * gated_recurrence: one CTA per (segment, head, 32 or 16 value columns). A thread owns one column j and every DS-th row of S in registers;
-//    the tokens of the segment are walked in order, sixteen at a time: the CTA first turns the sixteen tokens' projections into q, f
-//    and 1 - f in shared memory, then every thread updates its rows and adds its share of o[j], which a shuffle sums over the DS
-//    threads of the column. A decoded token is a segment of one: the cost is then the state's trip from memory and back.
+//  * gated_recurrence: one CTA per (segment, head, 32 or 16 value columns). A thread owns two neighbouring columns and RPT neighbouring rows of
+//    S in registers; the tokens of the segment are walked in order, sixteen at a time: the CTA first turns the sixteen tokens' projections
+//    into q, f and 1 - f in shared memory, then every thread updates its rows (the gates and queries of its rows come as 16-byte reads
+//    and serve both columns) and adds its share of o, which a shuffle sums over the DS threads of the column pair. The kernel is bound by
+//    instruction issue, not by memory: what counts is instructions per FMA. A decoded token is a segment of one: the cost is then the state's trip from memory and back.
 //    With `chunks` the same kernel walks chunks of a long segment instead, each from a zero state: it leaves the chunk's own
 //    outputs, its closing state and decay, and q_t times the decay from the chunk's start to t; `chunk_carry` then walks a segment's
 //    chunks in order (S_in of the next = decay * S_in + the chunk's closing state, elementwise, ending in the request's state) and
@@ -21,9 +22,9 @@ namespace {
 
 constexpr int kChunk = 16;   // tokens prepared at a time
 
-// RPT: rows of S a thread holds; kCols: value columns per CTA (32, or 16 where a thread holds sixteen rows: the CTA then has 512 threads at most)
+// RPT: rows of S a thread holds (for each of its two columns); kCols: value columns per CTA (32, or 16 where a thread holds sixteen rows)
 template <int RPT, int kCols>
-__global__ void __launch_bounds__(kCols * 32) gated_recurrence_kernel(const float* __restrict__ proj, int P, size_t stride_p, int R, const float* __restrict__ f_bias,
+__global__ void __launch_bounds__(kCols * 16) gated_recurrence_kernel(const float* __restrict__ proj, int P, size_t stride_p, int R, const float* __restrict__ f_bias,
                                         const float* __restrict__ lower, float* __restrict__ state, size_t slot_stride, const int* __restrict__ seg_start,
                                         const int* __restrict__ seg_slot, float* __restrict__ o_out, int heads, int D, int V, int DS,
                                         const int* __restrict__ seg_list, const int* __restrict__ chunks, float* __restrict__ chunk_state,
@@ -39,7 +40,9 @@ __global__ void __launch_bounds__(kCols * 32) gated_recurrence_kernel(const floa
   ib::pdl_launch_dependents();
   ib::pdl_wait();
   const int a = blockIdx.y, j0 = blockIdx.z * kCols;
-  const int tid = threadIdx.x, ds = tid % DS, col = tid / DS, j = j0 + col;
+  const int tid = threadIdx.x, ds = tid % DS, col = 2 * (tid / DS), j = j0 + col;   // columns j and j + 1, rows ds * RPT .. ds * RPT + RPT - 1
+  const int d0 = ds * RPT;
+  const bool d4 = D % 4 == 0;
   int t0, t1;
   float* S;
   if (chunks) {
@@ -52,11 +55,12 @@ __global__ void __launch_bounds__(kCols * 32) gated_recurrence_kernel(const floa
     t0 = seg_start[s], t1 = seg_start[s + 1];
     S = state + (size_t)seg_slot[s] * slot_stride + (size_t)a * D * V;
   }
-  float st[RPT];
+  float st[RPT][2];
 #pragma unroll
   for (int r = 0; r < RPT; r++) {
-    const int d = ds + r * DS;
-    st[r] = (!chunks && d < D && j < V) ? S[(size_t)d * V + j] : 0.f;
+    const int d = d0 + r;
+    st[r][0] = (!chunks && d < D && j < V) ? S[(size_t)d * V + j] : 0.f;
+    st[r][1] = (!chunks && d < D && j + 1 < V) ? S[(size_t)d * V + j + 1] : 0.f;
   }
   const int q_off = a * D, f_off = heads * D + a * D, v_off = 2 * heads * D + a * V + j0;
   for (int c0 = t0; c0 < t1; c0 += kChunk) {
@@ -97,27 +101,48 @@ __global__ void __launch_bounds__(kCols * 32) gated_recurrence_kernel(const floa
       }
     }
     for (int tt = 0; tt < n; tt++) {
-      const float vj = sv[tt * kCols + col];
-      const float* fq = sq + tt * D;
-      const float* ff = sf + tt * D;
-      const float* fg = sg + tt * D;
-      float acc = 0.f;
+      const float v0 = sv[tt * kCols + col], v1 = sv[tt * kCols + col + 1];
+      float f[RPT], g[RPT], q[RPT];
+      if (d4 && d0 + RPT <= D) {   // this thread's rows are whole groups of four: 16-byte reads
 #pragma unroll
-      for (int r = 0; r < RPT; r++) {
-        const int d = ds + r * DS;
-        if (d < D) {
-          st[r] = __fmaf_rn(ff[d], st[r], fg[d] * vj);
-          acc = __fmaf_rn(st[r], fq[d], acc);
+        for (int r = 0; r < RPT; r += 4) {
+          const float4 a = *(const float4*)(sf + tt * D + d0 + r), b = *(const float4*)(sg + tt * D + d0 + r), c = *(const float4*)(sq + tt * D + d0 + r);
+          f[r] = a.x, f[r + 1] = a.y, f[r + 2] = a.z, f[r + 3] = a.w;
+          g[r] = b.x, g[r + 1] = b.y, g[r + 2] = b.z, g[r + 3] = b.w;
+          q[r] = c.x, q[r + 1] = c.y, q[r + 2] = c.z, q[r + 3] = c.w;
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < RPT; r++) {
+          const int d = d0 + r;
+          const bool in = d < D;
+          f[r] = in ? sf[tt * D + d] : 0.f, g[r] = in ? sg[tt * D + d] : 0.f, q[r] = in ? sq[tt * D + d] : 0.f;
         }
       }
-      for (int o = DS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (ds == 0 && j < V) o_out[((size_t)(c0 + tt) * heads + a) * V + j] = acc;
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int r = 0; r < RPT; r++) {   // rows beyond D have f = g = q = 0: their state stays zero
+        st[r][0] = __fmaf_rn(f[r], st[r][0], g[r] * v0);
+        st[r][1] = __fmaf_rn(f[r], st[r][1], g[r] * v1);
+        acc0 = __fmaf_rn(st[r][0], q[r], acc0);
+        acc1 = __fmaf_rn(st[r][1], q[r], acc1);
+      }
+      for (int o = DS >> 1; o > 0; o >>= 1) {
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
+      }
+      if (ds == 0) {
+        float* dst = o_out + ((size_t)(c0 + tt) * heads + a) * V + j;
+        if (j < V) dst[0] = acc0;
+        if (j + 1 < V) dst[1] = acc1;
+      }
     }
   }
 #pragma unroll
   for (int r = 0; r < RPT; r++) {
-    const int d = ds + r * DS;
-    if (d < D && j < V) S[(size_t)d * V + j] = st[r];
+    const int d = d0 + r;
+    if (d < D && j < V) S[(size_t)d * V + j] = st[r][0];
+    if (d < D && j + 1 < V) S[(size_t)d * V + j + 1] = st[r][1];
   }
   if (chunks && blockIdx.z == 0) {
     __syncthreads();
@@ -232,12 +257,13 @@ extern "C" int ib_gated_recurrence(const float* proj, int P, long long stride_p,
   IB_CHECK_ARG(heads <= 65535 && (V + kCols - 1) / kCols <= 65535, "gated_recurrence: the grid is too large");
   int DS = 1;
   while (DS * rpt < D) DS *= 2;
+  if (DS < 2) DS = 2;   // a CTA is a whole warp at least (kCols / 2 column pairs x DS)
   const int R = 2 * heads * D + heads * V;
   const size_t smem = ((size_t)kChunk * (3 * D + kCols) + D) * sizeof(float);
   const dim3 grid((unsigned)n_segments, (unsigned)heads, (unsigned)((V + kCols - 1) / kCols));
   auto go = [&](auto kernel) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ib::launch(kernel, grid, kCols * DS, smem, stream, proj, P, (size_t)stride_p, R, f_bias, lower, state, (size_t)slot_stride, seg_start, seg_slot, o_out, heads, D, V, DS,
+    ib::launch(kernel, grid, kCols / 2 * DS, smem, stream, proj, P, (size_t)stride_p, R, f_bias, lower, state, (size_t)slot_stride, seg_start, seg_slot, o_out, heads, D, V, DS,
                seg_list, chunks, chunk_state, chunk_decay, qa);
   };
   if (rpt == 8) go(gated_recurrence_kernel<8, 32>);

@@ -10,6 +10,8 @@
 //    from its state slot by extra blocks of this kernel, so the convolution reads one array and its state update races with nothing.
 //  * causal_conv_rows: out[t] = h[t] + sum_j w[j, :] * h[t - taps + 1 + j] on that layout (w is [taps][channels]: a tap's weights lie together), and the request's new state (the last
 //    `halo` = taps - 1 rows of its extended run) written back to its slot.
+//  * add_layernorm_conv_single: both of the above in one kernel for a step in which every request brings one token (decoded tokens): a CTA
+//    per token norms its row, reads the request's `halo` state rows, writes the convolved row and shifts the state by one row.
 //  * depth_average: X = x[t] + scale * (sum_p delta[p][t] + bias); stack[k][t] = X; x[t] = sum_{j <= k} mix[j] * stack[j][t].
 //  * scale_values: v *= s (logits times a constant).
 #include <type_traits>
@@ -221,6 +223,102 @@ __global__ void __launch_bounds__(kLnThreads) causal_conv_rows_vec_kernel(const 
   }
 }
 
+template <typename O, bool VEC>
+__global__ void __launch_bounds__(kLnThreads) add_layernorm_conv_single_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride,
+                                                                               const float* __restrict__ dscale, const float* __restrict__ dbias,
+                                                                               const float* __restrict__ w, float eps, float* __restrict__ x_copy,
+                                                                               const float* __restrict__ cw, int taps, O* __restrict__ out, int H,
+                                                                               const int* __restrict__ seg_slot, float* __restrict__ state, size_t slot_stride) {
+  // Row t is segment t (one token each). As in causal_conv_rows_kernel the dependents do not start early. The row's sums are taken in the
+  // order of add_layernorm's kernels (the 16-byte form where that one runs, else the scalar form), so a
+  // decoded token's normed row has the same bits whichever kernel made it.
+  extern __shared__ __align__(16) float row[];
+  __shared__ float scratch[32];
+  ib::pdl_wait();
+  const int t = blockIdx.x, halo = taps - 1;
+  float* xr = x + (size_t)t * H;
+  auto value = [&](int i) {
+    float v = xr[i];
+    if (P > 0 || dbias) {
+      float d = dbias ? dbias[i] : 0.f;
+      if (P > 0) {
+        float a = delta[(size_t)t * H + i];
+        for (int p = 1; p < P; p++) a += delta[p * delta_stride + (size_t)t * H + i];
+        d = dbias ? a + d : a;
+      }
+      v = dscale ? __fmaf_rn(dscale[i], d, v) : v + d;
+      xr[i] = v;
+    }
+    if (x_copy) x_copy[(size_t)t * H + i] = v;
+    row[i] = v;
+    return v;
+  };
+  float* st = state + (size_t)seg_slot[t] * slot_stride;
+  if constexpr (VEC) {   // 16-byte accesses; every sum in the order of add_layernorm_vec_kernel and causal_conv_rows_vec_kernel
+    float sum = 0.f;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 v = ld4(xr + i);
+      if (P > 0 || dbias) {
+        float4 d = dbias ? ld4(dbias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (P > 0) {
+          float4 a = ld4(delta + (size_t)t * H + i);
+          for (int p = 1; p < P; p++) a = add4(a, ld4(delta + p * delta_stride + (size_t)t * H + i));
+          d = dbias ? add4(a, d) : a;
+        }
+        v = dscale ? fma4(ld4(dscale + i), d, v) : add4(v, d);
+        st4(xr + i, v);
+      }
+      if (x_copy) st4(x_copy + (size_t)t * H + i, v);
+      st4(row + i, v);
+      sum += (v.x + v.y) + (v.z + v.w);
+    }
+    const float mean = ib::block_sum(sum, scratch) / (float)H;
+    float sq = 0.f;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      const float4 v = ld4(row + i);
+      const float a = v.x - mean, b = v.y - mean, c = v.z - mean, e = v.w - mean;
+      sq = __fmaf_rn(e, e, __fmaf_rn(c, c, __fmaf_rn(b, b, __fmaf_rn(a, a, sq))));
+    }
+    const float inv = rsqrtf(ib::block_sum(sq, scratch) / (float)H + eps);
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      const float4 v = ld4(row + i), g = ld4(w + i);
+      const float4 h = make_float4((v.x - mean) * inv * g.x, (v.y - mean) * inv * g.y, (v.z - mean) * inv * g.z, (v.w - mean) * inv * g.w);
+      float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int j = 0; j < halo; j++) {
+        const float4 old = ld4(st + (size_t)j * H + i);
+        y = fma4(ld4(cw + (size_t)j * H + i), old, y);
+        if (j > 0) st4(st + (size_t)(j - 1) * H + i, old);
+      }
+      y = fma4(ld4(cw + (size_t)halo * H + i), h, y);
+      if (halo > 0) st4(st + (size_t)(halo - 1) * H + i, h);
+      st4(out + (size_t)t * H + i, add4(h, y));
+    }
+    return;
+  }
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) sum += value(i);
+  const float mean = ib::block_sum(sum, scratch) / (float)H;
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float c = row[i] - mean;
+    sq = __fmaf_rn(c, c, sq);
+  }
+  const float inv = rsqrtf(ib::block_sum(sq, scratch) / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float h = (row[i] - mean) * inv * w[i];
+    float y = 0.f;
+    for (int j = 0; j < halo; j++) {
+      const float old = st[(size_t)j * H + i];
+      y = __fmaf_rn(cw[(size_t)j * H + i], old, y);
+      if (j > 0) st[(size_t)(j - 1) * H + i] = old;
+    }
+    y = __fmaf_rn(cw[(size_t)halo * H + i], h, y);
+    if (halo > 0) st[(size_t)(halo - 1) * H + i] = h;
+    out[(size_t)t * H + i] = ib::from_f32<O>(h + y);
+  }
+}
+
+
 __global__ void depth_average_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride, const float* __restrict__ dscale,
                                          const float* __restrict__ dbias, float* __restrict__ stack, size_t layer_stride, int k, const float* __restrict__ mix, int H) {
   ib::pdl_wait();   // (no early start of the dependents: see depth_average_kernel)
@@ -276,6 +374,30 @@ extern "C" int ib_add_layernorm(float* x, const float* delta, int P, long long d
   else if (out_dtype == IB_F32) go(add_layernorm_kernel<float>, (float*)out);
   else go(add_layernorm_kernel<__nv_bfloat16>, (__nv_bfloat16*)out);
   IB_CHECK_LAUNCH("add_layernorm");
+  return 0;
+}
+
+extern "C" int ib_add_layernorm_conv_single(float* x, const float* delta, int P, long long delta_stride, const float* dscale, const float* dbias, const float* w,
+                                            float eps, float* x_copy, const float* cw, int taps, void* out, int out_dtype, int T, int H, const int* seg_slot, float* state,
+                                            long long slot_stride, cudaStream_t stream) {
+  if (T == 0) return 0;
+  IB_CHECK_ARG(T > 0 && H > 0 && P >= 0 && taps >= 1, "add_layernorm_conv_single: bad sizes T=%d H=%d P=%d taps=%d", T, H, P, taps);
+  const size_t smem = (size_t)H * sizeof(float);
+  IB_CHECK_ARG(smem <= 200 * 1024, "add_layernorm_conv_single: rows of %d values do not fit in shared memory", H);
+  auto go = [&](auto kernel, auto* o) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ib::launch(kernel, (unsigned)T, kLnThreads, smem, stream, x, delta, P, (size_t)delta_stride, dscale, dbias, w, eps, x_copy, cw, taps, o, H, seg_slot, state,
+               (size_t)slot_stride);
+  };
+  auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const bool vec = H % 4 == 0 && al(x) && al(delta) && delta_stride % 4 == 0 && al(dscale) && al(dbias) && al(w) && al(out) && al(x_copy) && al(state) && slot_stride % 4 == 0 &&
+                   al(cw);
+  if (out_dtype != IB_F32 && out_dtype != IB_BF16) return ib_set_error("add_layernorm_conv_single: unknown output dtype %d", out_dtype);
+  if (vec && out_dtype == IB_F32) go(add_layernorm_conv_single_kernel<float, true>, (float*)out);
+  else if (vec) go(add_layernorm_conv_single_kernel<__nv_bfloat16, true>, (__nv_bfloat16*)out);
+  else if (out_dtype == IB_F32) go(add_layernorm_conv_single_kernel<float, false>, (float*)out);
+  else go(add_layernorm_conv_single_kernel<__nv_bfloat16, false>, (__nv_bfloat16*)out);
+  IB_CHECK_LAUNCH("add_layernorm_conv_single");
   return 0;
 }
 

@@ -564,6 +564,35 @@ def causal_conv_rows(ext: torch.Tensor, w: torch.Tensor, out: torch.Tensor, layo
            layout.seg_start.data_ptr(), layout.seg_slot.data_ptr(), layout.n_segments, layout.state.data_ptr(), layout.slot_stride, _stream())
 
 
+L.register("ib_add_layernorm_conv_single", [L._p, L._p, L._i, L._ll, L._p, L._p, L._p, L._f, L._p, L._p, L._i, L._p, L._i, L._i, L._i, L._p, L._p, L._ll, L._p])
+
+
+def add_layernorm_conv_single(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, eps: float, conv_w: torch.Tensor, out: torch.Tensor, layout: ConvLayout,
+                              delta_scale: Optional[torch.Tensor] = None, delta_bias: Optional[torch.Tensor] = None, x_copy: Optional[torch.Tensor] = None) -> None:
+    """`add_layernorm` and `causal_conv_rows` in one kernel for a step whose segments all bring one token (row t is segment t): the normed row never
+    leaves the CTA, and the request's state rows are shifted by one. Sums run in the order of the two kernels."""
+    T, H = x.shape
+    _check("x", x, torch.float32)
+    _check("w", w, torch.float32, (H,))
+    _check("conv_w", conv_w, torch.float32, (layout.halo + 1, H))
+    _check("out", out, None, (T, H))
+    if layout.n_segments != T:
+        raise L.KernelError(f"add_layernorm_conv_single: {T} rows in {layout.n_segments} segments (every segment must bring one token)")
+    P = 0
+    if delta is not None:
+        _check("delta", delta, torch.float32)
+        if delta.dim() != 3 or tuple(delta.shape[1:]) != (T, H):
+            raise L.KernelError(f"delta must be [P, {T}, {H}], got {tuple(delta.shape)}")
+        P = delta.shape[0]
+    for name, v in (("delta_scale", delta_scale), ("delta_bias", delta_bias)):
+        if v is not None:
+            _check(name, v, torch.float32, (H,))
+    if x_copy is not None:
+        _check("x_copy", x_copy, torch.float32, (T, H))
+    L.call("ib_add_layernorm_conv_single", x.data_ptr(), _ptr(delta), P, T * H, _ptr(delta_scale), _ptr(delta_bias), w.data_ptr(), float(eps), _ptr(x_copy),
+           conv_w.data_ptr(), layout.halo + 1, out.data_ptr(), dtype_code(out.dtype), T, H, layout.seg_slot.data_ptr(), layout.state.data_ptr(), layout.slot_stride, _stream())
+
+
 def depth_average(x: torch.Tensor, delta: Optional[torch.Tensor], delta_scale: Optional[torch.Tensor], stack: torch.Tensor, k: int, mix: torch.Tensor,
                   delta_bias: Optional[torch.Tensor] = None) -> None:
     """X = x + delta_scale * (sum_p delta[p] + delta_bias); stack[k] = X; x = sum_{j <= k} mix[j] * stack[j] (in place). stack float32 [n, T, H], k >= 1."""

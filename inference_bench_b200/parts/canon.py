@@ -8,7 +8,7 @@ Layer i (counted from 0), with x the stream it is given, X_0 the embedding's out
 conv(h)_t = sum_k w[:, k] * h_(t - taps + 1 + k) per channel, zeros before a request's first token. The last taps - 1 normed rows of
 a request, for each of the two sublayers, are state (a fixed-size slot per request, beside the mixer's own cache or state).
 
-Kernels (csrc/layernorm.cu): `add_layernorm` adds the contribution before it with its scale and bias, norms, and lays the normed rows
+Kernels (csrc/layernorm.cu; a step whose requests all bring one token runs the first two as one, `add_layernorm_conv_single`): `add_layernorm` adds the contribution before it with its scale and bias, norms, and lays the normed rows
 out with every request's state rows in front of its tokens; `causal_conv_rows` convolves, rounds to the activation dtype and writes
 the new state; `depth_average` adds the feed-forward's contribution, files X_(i+1) and mixes. The results X_j of a step live in one
 buffer [layers + 1, T, H] kept in the step's memo.
@@ -71,8 +71,12 @@ class CanonBlock(base.Block, base.Part):
     def _read(self, ctx, norm, x, delta, scale, bias, conv_w, state, sublayer, x_copy=None):
         """The rows a sublayer reads: the contribution before it added to x, the norm, the convolution."""
         layout = self._layout(ctx, state, sublayer)
-        ext = norm.forward(ctx, x, delta, delta_scale=scale, delta_bias=bias, x_copy=x_copy, layout=layout)
         h = ctx.rt.empty((ctx.n_tokens, self.hidden))
+        if (ctx.fixed_shape or ctx.n_segments == ctx.n_tokens) and hasattr(norm, "eps") and getattr(norm, "w", None) is not None:
+            # a step of single tokens (decoded tokens): norm and convolution in one kernel, the normed row never leaves the CTA
+            ops.add_layernorm_conv_single(x, delta, norm.w, norm.eps, conv_w, h, layout, delta_scale=scale, delta_bias=bias, x_copy=x_copy)
+            return h
+        ext = norm.forward(ctx, x, delta, delta_scale=scale, delta_bias=bias, x_copy=x_copy, layout=layout)
         ops.causal_conv_rows(ext, conv_w, h, layout)
         return h
 

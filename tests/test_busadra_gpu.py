@@ -81,7 +81,7 @@ def test_layer_norm_convolution_and_its_state_over_portions(rt32, H, taps):
     halo = taps - 1
     state = torch.zeros((3, 2, max(halo, 1), H), device=DEV)     # [slots + scratch, sublayer, row, channel]
     state[:, 0] = 7.0                                            # the other sublayer's rows: never touched
-    plan = [[("a", 1), ("b", 2)], [("a", 2), ("b", 1)], [("a", 1)], [("a", 7), ("b", 6)], [("c", 1), ("a", 3)], [("c", 2), ("a", 9)], [("c", 11)]]
+    plan = [[("a", 1), ("b", 2)], [("a", 1), ("b", 1)], [("a", 2)], [("a", 7), ("b", 6)], [("c", 1), ("a", 3)], [("c", 2), ("a", 9)], [("c", 11)]]
     slot, at = {"a": 0, "b": 1, "c": 1}, {r: 0 for r in lens}
     for step in plan:
         if step[0][0] == "c" and at["c"] == 0:
@@ -91,6 +91,13 @@ def test_layer_norm_convolution_and_its_state_over_portions(rt32, H, taps):
         xs = torch.cat([x[r][at[r]:at[r] + n] for r, n in step]).to(DEV).contiguous()
         ds = torch.cat([delta[r][:, at[r]:at[r] + n] for r, n in step], dim=1).to(DEV).contiguous()
         lay = ops.ConvLayout(halo, ctx.seg_of_token, ctx.seg_start, ctx.seg_slot, len(step), state[:, 1], state.stride(0))
+        single = None
+        if all(n == 1 for _, n in step):   # a step of single tokens: the one-kernel form gives the bits of the two kernels, and the same state
+            x1, st1 = xs.clone(), state.clone()
+            lay1 = ops.ConvLayout(halo, ctx.seg_of_token, ctx.seg_start, ctx.seg_slot, len(step), st1[:, 1], st1.stride(0))
+            single = torch.empty((xs.shape[0], H), device=DEV)
+            ops.add_layernorm_conv_single(x1, ds, _f32(w), eps, _f32(cw.t()), single, lay1, delta_scale=_f32(scale), delta_bias=_f32(bias))
+            single = (single, x1, st1)
         ext = torch.empty((lay.rows(xs.shape[0]), H), device=DEV)
         ops.add_layernorm(xs, ds, _f32(w), ext, eps, None, _f32(scale), _f32(bias), None, lay)
         for dt, tol in ((torch.float32, 3e-5), (torch.bfloat16, 3e-2)):
@@ -98,6 +105,8 @@ def test_layer_norm_convolution_and_its_state_over_portions(rt32, H, taps):
             saved = state.clone()
             ops.causal_conv_rows(ext, _f32(cw.t()), out, lay)
             if dt == torch.float32:
+                if single is not None:
+                    assert torch.equal(single[0], out) and torch.equal(single[1], xs) and torch.equal(single[2], state)
                 state.copy_(saved)       # the second pass writes the same state again
             o = 0
             for r, n in step:
