@@ -427,7 +427,7 @@ DESIGN_KINDS = {   # kinds of kernel by the library entry points that launch the
                 "recurrence": ["ib_gated_recurrence", "ib_recurrence_chunks_finish", "ib_head_rmsnorm"],
                 "experts": ["ib_gemm_grouped", "ib_gemm_grouped_mma", "ib_gemm_grouped_tcgen05", "ib_gemm_grouped_swiglu_tcgen05", "ib_scatter_scaled_rows"],
                 "route": ["ib_moe_route", "ib_moe_sort", "ib_moe_combine"],
-                "norm": ["ib_add_layernorm", "ib_causal_conv_rows", "ib_depth_average", "ib_qk_norm_rope_kv"], "gemm": LEAVE_OUT["gemm"]},
+                "norm": ["ib_add_layernorm", "ib_causal_conv_rows", "ib_add_layernorm_conv_single", "ib_depth_average", "ib_qk_norm_rope_kv"], "gemm": LEAVE_OUT["gemm"]},
 }
 # Busadra at layer sizes that resemble small hybrid models: windowed grouped-query attention with heads of 128, a gated linear recurrence
 # whose heads hold a 128 x 128 state, and routed experts; layers in the order attention, recurrence, recurrence, attention (repeated).
