@@ -170,7 +170,8 @@ def _fill(pool, perm, page, k, v):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,page,window,cap,sink", [
     (4, 2, 32, 16, 16, 24, 8.0, True), (6, 6, 24, 40, 8, None, 15.0, True), (8, 2, 64, 64, 32, 48, 50.0, True), (4, 1, 128, 128, 16, 17, 10.0, True),
-    (6, 6, 64, 64, 16, 96, 20.0, True), (3, 1, 16, 16, 8, 13, None, True), (8, 2, 64, 64, 16, 40, 6.0, False), (8, 8, 64, 64, 64, 64, None, False)])
+    (6, 6, 64, 64, 16, 96, 20.0, True), (3, 1, 16, 16, 8, 13, None, True), (8, 2, 64, 64, 16, 40, 6.0, False), (8, 8, 64, 64, 64, 64, None, False),
+    (8, 2, 64, 64, 16, 40, None, True), (4, 4, 128, 128, 32, None, None, True), (32, 1, 64, 64, 16, 70, 12.0, True)])
 def test_attention_windows_far_keys_page_borders_caps_and_the_sink(rt32, rt16, dtype, heads, kv_heads, dim, vdim, page, window, cap, sink):
     """One key is made to stand out for one query (they share a large entry): the last key inside the window and the first outside it,
     the keys on both sides of a page border, a key far back, the query's own position and the one after it; for rows of a prompt
@@ -247,7 +248,7 @@ def test_projection_rows_get_their_bias_and_rotation_and_reach_the_cache(rt32, h
 
 
 # ------------------------------------------------------------------------------------------ recurrence
-@pytest.mark.parametrize("heads,D,V", [(3, 16, 24), (1, 48, 20), (4, 64, 64), (2, 40, 8), (2, 300, 33), (2, 128, 256)])
+@pytest.mark.parametrize("heads,D,V", [(3, 16, 24), (1, 48, 20), (4, 64, 64), (2, 40, 8), (2, 300, 33), (2, 128, 256), (2, 10, 7), (1, 6, 1)])
 def test_recurrence_over_portions_slots_and_long_decoding(rt32, heads, D, V):
     """Two requests advance in one batch in portions of 1, 2, 17 and more tokens (beyond the sixteen the kernel prepares at a time),
     then one of them decodes 150 tokens one by one; a third request takes a freed slot that is zeroed. Gates near 1 for some channels
