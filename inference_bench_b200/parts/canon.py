@@ -36,8 +36,11 @@ class CanonBlock(base.Block, base.Part):
         base.Block.__init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward)
         if taps < 1 or not 0 <= index < depth:
             raise ValueError(f"taps {taps} must be at least 1 and layer {index} one of {depth}")
-        self.prefix, self.hidden, self.taps, self.index, self.depth, self.names = prefix, hidden, taps, index, depth, tuple(names)
         self.has_ff = not isinstance(feed_forward, NoFeedForward)
+        for norm in (mixer_norm, feed_forward_norm) if self.has_ff else (mixer_norm,):
+            if not getattr(norm, "takes_layout", False):
+                raise ValueError(f"this arrangement needs norms that lay their rows out for the convolution (layernorm does); {type(norm).__name__} does not")
+        self.prefix, self.hidden, self.taps, self.index, self.depth, self.names = prefix, hidden, taps, index, depth, tuple(names)
         self.ls1 = self.ls2 = self.conv1 = self.conv2 = self.mix = None
 
     # ------------------------------------------------------------ as a part: its own tensors and state
@@ -72,7 +75,7 @@ class CanonBlock(base.Block, base.Part):
         """The rows a sublayer reads: the contribution before it added to x, the norm, the convolution."""
         layout = self._layout(ctx, state, sublayer)
         h = ctx.rt.empty((ctx.n_tokens, self.hidden))
-        if (ctx.fixed_shape or ctx.n_segments == ctx.n_tokens) and hasattr(norm, "eps") and getattr(norm, "w", None) is not None:
+        if ctx.fixed_shape or ctx.n_segments == ctx.n_tokens:
             # a step of single tokens (decoded tokens): norm and convolution in one kernel, the normed row never leaves the CTA
             ops.add_layernorm_conv_single(x, delta, norm.w, norm.eps, conv_w, h, layout, delta_scale=scale, delta_bias=bias, x_copy=x_copy)
             return h

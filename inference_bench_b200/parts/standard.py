@@ -55,6 +55,8 @@ class LayerNorm(base.Norm):
     copy of the updated stream, and a layout of the normed rows for a convolution over time (`ops.ConvLayout`; the rows then stay
     float32 and keep their place in that layout)."""
 
+    takes_layout = True   # `forward` takes the extras named above (what a block with input convolutions asks of its norms)
+
     def __init__(self, name: str, size: int, eps: float):
         self.name, self.size, self.eps = name, size, eps
         self.w: Optional[torch.Tensor] = None
